@@ -1,0 +1,283 @@
+"""Python host layer over the C ABI.
+
+Argument order follows the operand lists of `sparsewave.spmv`,
+`sparsewave.spmm` and `sparsewave.bsr_spmm` (row offsets, column indices,
+values, dense input, output; include/.../IR/SparseWaveOps.td:37-43,108-115,
+149-159 in the SparseWave tree) and options are written in the reference's
+own spelling, e.g. ``"spmv-mapping=wave-per-row spmv-block-size=128"``.
+
+PyTorch tensors are used for device memory and streams only; every operator
+call goes to libsparsewave_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import SwbLaunchShape, SwbOptions
+
+
+class SparseWaveError(RuntimeError):
+    """A C-ABI call returned a non-zero status; `.status` holds it."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+def make_options(text: str = "", **fields) -> SwbOptions:
+    """Default options, then `text` (reference spelling), then field overrides."""
+    lib = _lib.load()
+    o = SwbOptions()
+    lib.swb_options_default(C.byref(o))
+    if text:
+        st = lib.swb_options_parse(None, C.byref(o), text.encode())
+        if st != 0:
+            raise SparseWaveError(st, lib.swb_last_error(None).decode())
+    for k, v in fields.items():
+        if not hasattr(o, k):
+            raise AttributeError(f"swb_options has no field {k!r}")
+        setattr(o, k, v)
+    return o
+
+
+def _dev_ptr(t: Optional[torch.Tensor], dtype: torch.dtype, name: str) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise TypeError(f"{name} must be contiguous")
+    return t.data_ptr() if t.numel() > 0 else (t.data_ptr() or None)
+
+
+def _host_ptr(a, dtype, name: str) -> Optional[int]:
+    if isinstance(a, torch.Tensor):
+        if a.is_cuda:
+            raise TypeError(f"{name} must be a host tensor")
+        if a.dtype != dtype or not a.is_contiguous():
+            raise TypeError(f"{name} must be a contiguous {dtype} tensor")
+        return a.data_ptr() or None
+    np_dtype = {torch.int32: np.int32, torch.float32: np.float32, torch.uint16: np.uint16,
+                torch.bfloat16: np.uint16, torch.int64: np.int64}[dtype]
+    if not isinstance(a, np.ndarray) or a.dtype != np_dtype or not a.flags["C_CONTIGUOUS"]:
+        raise TypeError(f"{name} must be a C-contiguous numpy array of {np_dtype}")
+    return a.ctypes.data or None
+
+
+class Context:
+    """One swb_context: one host thread, one CUDA device."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load()
+        self._ctx = C.c_void_p()
+        st = self._lib.swb_create(C.byref(self._ctx), int(device))
+        if st != 0:
+            raise SparseWaveError(st, self._lib.swb_last_error(None).decode())
+        self.device = int(device)
+
+    def close(self) -> None:
+        if self._ctx:
+            self._lib.swb_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # -- helpers --------------------------------------------------------------
+    def _check(self, st: int) -> None:
+        if st != 0:
+            raise SparseWaveError(st, self._lib.swb_last_error(self._ctx).decode())
+
+    @staticmethod
+    def _opts(options) -> SwbOptions:
+        if isinstance(options, SwbOptions):
+            return options
+        return make_options(options or "")
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    @property
+    def kernel_launches(self) -> int:
+        return int(self._lib.swb_kernel_launch_count(self._ctx))
+
+    def validate(self, options) -> None:
+        self._check(self._lib.swb_options_validate(self._ctx, C.byref(self._opts(options))))
+
+    def launch_shape(self, options, rows: int, nnz: int, n_rhs: int = 0) -> SwbLaunchShape:
+        out = SwbLaunchShape()
+        self._check(self._lib.swb_launch_shape_query(self._ctx, C.byref(self._opts(options)), rows, nnz, n_rhs,
+                                                     C.byref(out)))
+        return out
+
+    # -- operators on device tensors ---------------------------------------------
+    def spmv(self, options, row_ptr, col_idx, val, x, y=None, *, rows=None):
+        """y = A @ x for CSR A; returns y (allocated when not given)."""
+        rows = int(row_ptr.numel() - 1 if rows is None else rows)
+        cols, nnz = int(x.numel()), int(val.numel())
+        if y is None:
+            y = torch.empty(rows, dtype=torch.float32, device=x.device)
+        o = self._opts(options)
+        self._check(self._lib.swb_spmv(
+            self._ctx, C.byref(o), rows, cols, nnz,
+            _dev_ptr(row_ptr, torch.int32, "row_ptr"), _dev_ptr(col_idx, torch.int32, "col_idx"),
+            _dev_ptr(val, torch.float32, "val"), _dev_ptr(x, torch.float32, "x"),
+            _dev_ptr(y, torch.float32, "y"), self._stream()))
+        return y
+
+    def spmv_position_trace(self, options, row_ptr, col_idx, val, x):
+        """Position-mapped SpMV that also returns (row, worker, segment_end) per position."""
+        rows, cols, nnz = int(row_ptr.numel() - 1), int(x.numel()), int(val.numel())
+        y = torch.empty(rows, dtype=torch.float32, device=x.device)
+        tr = [torch.full((max(nnz, 1),), -1, dtype=torch.int32, device=x.device) for _ in range(3)]
+        o = self._opts(options)
+        self._check(self._lib.swb_spmv_position_trace(
+            self._ctx, C.byref(o), rows, cols, nnz,
+            _dev_ptr(row_ptr, torch.int32, "row_ptr"), _dev_ptr(col_idx, torch.int32, "col_idx"),
+            _dev_ptr(val, torch.float32, "val"), _dev_ptr(x, torch.float32, "x"),
+            _dev_ptr(y, torch.float32, "y"), tr[0].data_ptr(), tr[1].data_ptr(), tr[2].data_ptr(),
+            self._stream()))
+        return y, tr[0][:nnz], tr[1][:nnz], tr[2][:nnz]
+
+    def spmm(self, options, row_ptr, col_idx, val, B, C_out=None, *, rows=None):
+        """C = A @ B for CSR A and row-major dense B (cols x N)."""
+        rows = int(row_ptr.numel() - 1 if rows is None else rows)
+        cols, n_rhs, nnz = int(B.shape[0]), int(B.shape[1]), int(val.numel())
+        if C_out is None:
+            C_out = torch.empty((rows, n_rhs), dtype=torch.float32, device=B.device)
+        o = self._opts(options)
+        self._check(self._lib.swb_spmm(
+            self._ctx, C.byref(o), rows, cols, nnz, n_rhs,
+            _dev_ptr(row_ptr, torch.int32, "row_ptr"), _dev_ptr(col_idx, torch.int32, "col_idx"),
+            _dev_ptr(val, torch.float32, "val"), _dev_ptr(B, torch.float32, "B"),
+            _dev_ptr(C_out, torch.float32, "C"), self._stream()))
+        return C_out
+
+    def bsr_spmm(self, options, block_row_ptr, block_col_idx, block_values, B, block_size: int, C_out=None):
+        """C = A @ B for BSR A; f32 or bf16 chosen by the dtype of block_values."""
+        brows = int(block_row_ptr.numel() - 1)
+        rows, cols, n_rhs = brows * block_size, int(B.shape[0]), int(B.shape[1])
+        nnzb = int(block_col_idx.numel())
+        dt = block_values.dtype
+        if dt not in (torch.float32, torch.bfloat16):
+            raise TypeError("block_values must be float32 or bfloat16")
+        if int(block_values.numel()) != nnzb * block_size * block_size:
+            raise SparseWaveError(_lib.SWB_ERR_INVALID_SHAPE,
+                                  "block values size must equal the number of blocks times block_size squared, "
+                                  f"but got {int(block_values.numel())} and {nnzb} blocks")
+        if C_out is None:
+            C_out = torch.empty((rows, n_rhs), dtype=dt, device=B.device)
+        fn = self._lib.swb_bsr_spmm_f32 if dt == torch.float32 else self._lib.swb_bsr_spmm_bf16
+        o = self._opts(options)
+        self._check(fn(self._ctx, C.byref(o), rows, cols, nnzb, block_size, n_rhs,
+                       _dev_ptr(block_row_ptr, torch.int32, "block_row_ptr"),
+                       _dev_ptr(block_col_idx, torch.int32, "block_col_idx"),
+                       _dev_ptr(block_values, dt, "block_values"), _dev_ptr(B, dt, "B"),
+                       _dev_ptr(C_out, dt, "C"), self._stream()))
+        return C_out
+
+    def bundle_launch(self, operation: str, n: int, args) -> None:
+        """lrrt-style launch: five device pointers (rowOffsets, columnIndices, values, rhs, output)."""
+        arr = (C.c_void_p * 5)(*[a.data_ptr() if isinstance(a, torch.Tensor) else a for a in args])
+        self._check(self._lib.swb_bundle_launch(self._ctx, operation.encode(), int(n), arr, self._stream()))
+
+    # -- operators on host buffers --------------------------------------------------
+    def spmv_host(self, options, row_ptr, col_idx, val, x, y):
+        rows, cols, nnz = len(row_ptr) - 1, len(x), len(val)
+        o = self._opts(options)
+        self._check(self._lib.swb_spmv_host(
+            self._ctx, C.byref(o), rows, cols, nnz, _host_ptr(row_ptr, torch.int32, "row_ptr"),
+            _host_ptr(col_idx, torch.int32, "col_idx"), _host_ptr(val, torch.float32, "val"),
+            _host_ptr(x, torch.float32, "x"), _host_ptr(y, torch.float32, "y")))
+        return y
+
+    def spmm_host(self, options, row_ptr, col_idx, val, B, C_out):
+        rows, cols, n_rhs, nnz = len(row_ptr) - 1, B.shape[0], B.shape[1], len(val)
+        o = self._opts(options)
+        self._check(self._lib.swb_spmm_host(
+            self._ctx, C.byref(o), rows, cols, nnz, n_rhs, _host_ptr(row_ptr, torch.int32, "row_ptr"),
+            _host_ptr(col_idx, torch.int32, "col_idx"), _host_ptr(val, torch.float32, "val"),
+            _host_ptr(B, torch.float32, "B"), _host_ptr(C_out, torch.float32, "C")))
+        return C_out
+
+    def bsr_spmm_bf16_host(self, options, block_row_ptr, block_col_idx, block_values, B, block_size, C_out):
+        brows = len(block_row_ptr) - 1
+        rows, cols, n_rhs, nnzb = brows * block_size, B.shape[0], B.shape[1], len(block_col_idx)
+        o = self._opts(options)
+        self._check(self._lib.swb_bsr_spmm_bf16_host(
+            self._ctx, C.byref(o), rows, cols, nnzb, block_size, n_rhs,
+            _host_ptr(block_row_ptr, torch.int32, "block_row_ptr"),
+            _host_ptr(block_col_idx, torch.int32, "block_col_idx"),
+            _host_ptr(block_values, torch.bfloat16, "block_values"), _host_ptr(B, torch.bfloat16, "B"),
+            _host_ptr(C_out, torch.bfloat16, "C")))
+        return C_out
+
+    def check_csr_host(self, rows, cols, row_ptr, col_idx) -> None:
+        self._check(self._lib.swb_check_csr_host(self._ctx, rows, cols, len(col_idx),
+                                                 _host_ptr(row_ptr, torch.int32, "row_ptr"),
+                                                 _host_ptr(col_idx, torch.int32, "col_idx")))
+
+
+# -- context-free helpers (host arithmetic only; need no GPU) ---------------------------
+
+def partition(lower: int, upper: int, worker: int, count: int) -> tuple[int, int]:
+    b, e = C.c_int64(), C.c_int64()
+    _lib.load().swb_partition(lower, upper, worker, count, C.byref(b), C.byref(e))
+    return b.value, e.value
+
+
+def chunk_bounds(lower: int, upper: int, worker: int, factor: int) -> tuple[int, int]:
+    b, e = C.c_int64(), C.c_int64()
+    _lib.load().swb_chunk_bounds(lower, upper, worker, factor, C.byref(b), C.byref(e))
+    return b.value, e.value
+
+
+def row_at_position(row_ptr: np.ndarray, position: int) -> int:
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    return int(_lib.load().swb_row_at_position(row_ptr.ctypes.data, len(row_ptr), position))
+
+
+def shard_rows_by_nnz(row_ptr: np.ndarray, n_shards: int) -> np.ndarray:
+    """nnz-balanced contiguous row shard boundaries (n_shards + 1 entries)."""
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    out = np.zeros(n_shards + 1, dtype=np.int64)
+    lib = _lib.load()
+    st = lib.swb_shard_rows_by_nnz(None, row_ptr.ctypes.data, len(row_ptr) - 1, n_shards, out.ctypes.data)
+    if st != 0:
+        raise SparseWaveError(st, lib.swb_last_error(None).decode())
+    return out
+
+
+def launch_shape(options, rows: int, nnz: int, n_rhs: int = 0) -> SwbLaunchShape:
+    """Launch geometry without a context (auto batch assumes 148 SMs)."""
+    lib = _lib.load()
+    o = options if isinstance(options, SwbOptions) else make_options(options or "")
+    out = SwbLaunchShape()
+    st = lib.swb_launch_shape_query(None, C.byref(o), rows, nnz, n_rhs, C.byref(out))
+    if st != 0:
+        raise SparseWaveError(st, lib.swb_last_error(None).decode())
+    return out
+
+
+def validate_options(options) -> None:
+    lib = _lib.load()
+    o = options if isinstance(options, SwbOptions) else make_options(options or "")
+    st = lib.swb_options_validate(None, C.byref(o))
+    if st != 0:
+        raise SparseWaveError(st, lib.swb_last_error(None).decode())

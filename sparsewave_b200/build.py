@@ -1,0 +1,83 @@
+"""Builds libsparsewave_b200.so in-tree with nvcc for sm_100a.
+
+`python -m sparsewave_b200.build` compiles every translation unit under
+`csrc/` to an object file and links them into
+`sparsewave_b200/lib/libsparsewave_b200.so`.  Objects whose sources (and the
+headers they include) are older than the object are not recompiled.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+LIBDIR = PKG / "lib"
+OBJDIR = PKG / "lib" / "obj"
+LIB = LIBDIR / "libsparsewave_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden",
+    "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(nvcc).exists():
+        raise RuntimeError("nvcc not found; libsparsewave_b200.so cannot be built")
+    return nvcc
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _headers() -> list[Path]:
+    return sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + sorted((ROOT / "include").glob("*.h"))
+
+
+def _stale(target: Path, deps: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in deps)
+
+
+def _compile(src: Path, verbose: bool, extra: list[str]) -> Path:
+    obj = OBJDIR / (src.stem + ".o")
+    if _stale(obj, [src, Path(__file__)] + _headers()):
+        cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(ROOT / "include"), "-c", str(src), "-o", str(obj)]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+    return obj
+
+
+def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
+    """Compiles and links the library; returns its path."""
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    extra = ["-Xptxas", "-v"] if ptxas_info else []
+    srcs = sources()
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, verbose, extra), srcs))
+    if _stale(LIB, objs):
+        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-lcuda"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    if "--clean" in sys.argv and OBJDIR.exists():
+        shutil.rmtree(OBJDIR)
+    path = build(verbose=True, ptxas_info="--ptxas-info" in sys.argv)
+    print(path)

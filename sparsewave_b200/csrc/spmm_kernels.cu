@@ -1,0 +1,269 @@
+// CSR SpMM kernels for sm_100a: thread-per-output, wave-per-row-tile and
+// thread-per-position mappings of sparsewave.spmm.  B is cols x N and C is
+// rows x N, row-major.  Products and sums are separate f32 operations.
+#include "swb_index.h"
+#include "swb_kernels.h"
+
+namespace swb {
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+__device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+
+// ---------------------------------------------------------------------------
+// thread-per-output (ThreadPerOutputSpMMPattern, SparseWaveToGPU.cpp:489-558)
+// element = blockIdx * blockDim + threadIdx; row = element / N; column =
+// element % N; sequential sum in position order (bit-identical to the CPU
+// CSR loop).
+// ---------------------------------------------------------------------------
+__global__ void spmm_thread_per_output_kernel(int64_t rows, int64_t N,
+                                              const int32_t *__restrict__ row_ptr,
+                                              const int32_t *__restrict__ col,
+                                              const float *__restrict__ val,
+                                              const float *__restrict__ B, float *__restrict__ C) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= rows * N) return;
+  const int64_t row = e / N, j = e % N;
+  int p = row_ptr[row];
+  const int end = row_ptr[row + 1];
+  const float *Bj = B + j;
+  float sum = 0.0f;
+  for (; p + 4 <= end; p += 4) {
+    int c0 = __ldg(col + p), c1 = __ldg(col + p + 1), c2 = __ldg(col + p + 2), c3 = __ldg(col + p + 3);
+    float v0 = __ldg(val + p), v1 = __ldg(val + p + 1), v2 = __ldg(val + p + 2), v3 = __ldg(val + p + 3);
+    float b0 = __ldg(Bj + (int64_t)c0 * N), b1 = __ldg(Bj + (int64_t)c1 * N);
+    float b2 = __ldg(Bj + (int64_t)c2 * N), b3 = __ldg(Bj + (int64_t)c3 * N);
+    sum = add(sum, mul(v0, b0));
+    sum = add(sum, mul(v1, b1));
+    sum = add(sum, mul(v2, b2));
+    sum = add(sum, mul(v3, b3));
+  }
+  for (; p < end; ++p) sum = add(sum, mul(__ldg(val + p), __ldg(Bj + (int64_t)__ldg(col + p) * N)));
+  C[e] = sum;
+}
+
+// ---------------------------------------------------------------------------
+// wave-per-row-tile (WavePerRowTileSpMMPattern, SparseWaveToGPU.cpp:1057-1256)
+// tiles = ceil(N / T); unit = blockIdx * (blockDim/32) + threadIdx/32;
+// row = unit / tiles; tile = unit % tiles; first column = tile * T.  Lanes
+// stride the row's positions; each position's value is loaded once and used
+// for the T right-hand-side columns of the tile.  A tile that reaches past N
+// runs the guarded path.
+//
+// TCAP is T rounded up to a power of two.  When T == TCAP, T % 4 == 0,
+// N % 4 == 0 and B, C are 16-byte aligned, the T floats of a B row are read
+// with 128-bit loads and the result is written with 128-bit stores.
+//
+// Reduction: instead of T independent 5-step butterflies (5*T shuffles) the
+// warp does a halving exchange: at the step with lane distance `off` each
+// lane keeps one half of its accumulators and sends the other half to its
+// partner, so the accumulator count halves per step until one is left
+// (TCAP-1 shuffles), then plain butterfly steps finish.  Lane l ends with the
+// full sum of column (l >> (5 - log2 TCAP)) of the tile.
+// ---------------------------------------------------------------------------
+template <int TCAP>
+__device__ __forceinline__ void tile_reduce(float (&acc)[TCAP], int lane) {
+  int w = TCAP;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    if (w > 1) {
+      const int half = w >> 1;
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < TCAP / 2; ++i) {
+        if (i < half) {
+          const float send = upper ? acc[i] : acc[i + half];
+          const float keep = upper ? acc[i + half] : acc[i];
+          acc[i] = add(keep, __shfl_xor_sync(FULL, send, off));
+        }
+      }
+      w = half;
+    } else {
+      acc[0] = add(acc[0], __shfl_xor_sync(FULL, acc[0], off));
+    }
+  }
+}
+
+// Column (within the tile) whose sum lane `lane` holds after tile_reduce.
+template <int TCAP>
+__device__ __forceinline__ int tile_column_of_lane(int lane) {
+  int k = 0, w = TCAP;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    if (w > 1) {
+      w >>= 1;
+      if (lane & off) k += w;
+    }
+  }
+  return k;
+}
+
+// Lowest lane holding column k: the lanes whose "kept" bits spell k and whose
+// remaining low bits are zero.
+template <int TCAP>
+__device__ __forceinline__ bool lane_is_column_writer(int lane) {
+  int w = TCAP, used = 0;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    if (w > 1) {
+      w >>= 1;
+      used |= off;
+    }
+  }
+  return (lane & ~used) == 0;
+}
+
+template <int TCAP, bool VEC>
+__global__ void spmm_wave_per_row_tile_kernel(int64_t rows, int64_t N, int T, int64_t tiles,
+                                              const int32_t *__restrict__ row_ptr,
+                                              const int32_t *__restrict__ col,
+                                              const float *__restrict__ val,
+                                              const float *__restrict__ B, float *__restrict__ C) {
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * tiles) return;
+  const int64_t row = unit / tiles;
+  const int64_t j0 = (unit % tiles) * T;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  const bool full = j0 + T <= N;
+
+  float acc[TCAP];
+#pragma unroll
+  for (int k = 0; k < TCAP; ++k) acc[k] = 0.0f;
+
+  if (VEC) {  // implies T == TCAP, full tiles only, aligned
+    for (int p = start + lane; p < end; p += 32) {
+      const int c = __ldcs(col + p);
+      const float v = __ldcs(val + p);
+      const float4 *b4 = reinterpret_cast<const float4 *>(B + (int64_t)c * N + j0);
+#pragma unroll
+      for (int q = 0; q < TCAP / 4; ++q) {
+        const float4 b = __ldg(b4 + q);
+        acc[4 * q + 0] = add(acc[4 * q + 0], mul(v, b.x));
+        acc[4 * q + 1] = add(acc[4 * q + 1], mul(v, b.y));
+        acc[4 * q + 2] = add(acc[4 * q + 2], mul(v, b.z));
+        acc[4 * q + 3] = add(acc[4 * q + 3], mul(v, b.w));
+      }
+    }
+  } else if (full && T == TCAP) {
+    for (int p = start + lane; p < end; p += 32) {
+      const int c = __ldcs(col + p);
+      const float v = __ldcs(val + p);
+      const float *b = B + (int64_t)c * N + j0;
+#pragma unroll
+      for (int k = 0; k < TCAP; ++k) acc[k] = add(acc[k], mul(v, __ldg(b + k)));
+    }
+  } else {
+    // Guarded path: tail tile (or T below the register capacity).
+    for (int p = start + lane; p < end; p += 32) {
+      const int c = __ldcs(col + p);
+      const float v = __ldcs(val + p);
+      const float *b = B + (int64_t)c * N + j0;
+#pragma unroll
+      for (int k = 0; k < TCAP; ++k)
+        if (k < T && j0 + k < N) acc[k] = add(acc[k], mul(v, __ldg(b + k)));
+    }
+  }
+
+  tile_reduce<TCAP>(acc, lane);
+  const int k = tile_column_of_lane<TCAP>(lane);
+  if (lane_is_column_writer<TCAP>(lane) && k < T && j0 + k < N) C[row * N + j0 + k] = acc[0];
+}
+
+// ---------------------------------------------------------------------------
+// thread-per-position (DecomposePositionSpMMPattern,
+// PositionSpMMDecomposition.cpp:19-73, scheduled with the thread/atomic
+// schedule, Pipelines.cpp:262-271).  The iteration space is [0, nnz*N):
+// position = i / N, column = i % N, key = row*N + column; worker w owns
+// iterations [w*chunk, min(nnz*N, (w+1)*chunk)) and issues one atomicAdd per
+// iteration.
+// ---------------------------------------------------------------------------
+__global__ void spmm_thread_per_position_kernel(int64_t rows, int64_t nnz, int64_t N, int64_t chunk,
+                                                const int32_t *__restrict__ row_ptr,
+                                                const int32_t *__restrict__ col,
+                                                const float *__restrict__ val,
+                                                const float *__restrict__ B, float *__restrict__ C) {
+  const int64_t worker = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t begin, end;
+  chunk_bounds(0, nnz * N, worker, chunk, begin, end);
+  if (begin >= end) return;
+  int64_t p = begin / N, j = begin % N;
+  int64_t row = row_at_position(row_ptr, rows + 1, p);
+  int64_t next = row_ptr[row + 1];
+  int c = __ldg(col + p);
+  float v = __ldg(val + p);
+  for (int64_t i = begin; i < end; ++i) {
+    atomicAdd(C + row * N + j, mul(v, __ldg(B + (int64_t)c * N + j)));
+    if (++j == N) {
+      j = 0;
+      ++p;
+      if (i + 1 < end) {
+        while (next <= p) {
+          ++row;
+          next = row_ptr[row + 1];
+        }
+        c = __ldg(col + p);
+        v = __ldg(val + p);
+      }
+    }
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int TCAP>
+cudaError_t launch_tile(const CsrSpmmArgs &a, int block, int T, cudaStream_t s) {
+  const int64_t tiles = ceil_div(a.n_rhs, T);
+  const int64_t units = a.rows * tiles;
+  const unsigned grid = (unsigned)max1(ceil_div(units, block / 32));
+  const bool vec = (T == TCAP) && (TCAP % 4 == 0) && (a.n_rhs % 4 == 0) && (a.n_rhs % T == 0) &&
+                   aligned16(a.B) && aligned16(a.C);
+  if (vec) {
+    if constexpr (TCAP >= 4)
+      spmm_wave_per_row_tile_kernel<TCAP, true><<<grid, block, 0, s>>>(
+          a.rows, a.n_rhs, T, tiles, a.row_ptr, a.col_idx, a.val, a.B, a.C);
+  } else {
+    spmm_wave_per_row_tile_kernel<TCAP, false><<<grid, block, 0, s>>>(
+        a.rows, a.n_rhs, T, tiles, a.row_ptr, a.col_idx, a.val, a.B, a.C);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block, cudaStream_t s,
+                                          int64_t *launches) {
+  const unsigned grid = (unsigned)max1(ceil_div(a.rows * a.n_rhs, block));
+  spmm_thread_per_output_kernel<<<grid, block, 0, s>>>(a.rows, a.n_rhs, a.row_ptr, a.col_idx,
+                                                       a.val, a.B, a.C);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int tile,
+                                          cudaStream_t s, int64_t *launches) {
+  ++*launches;
+  if (tile <= 1) return launch_tile<1>(a, block, tile, s);
+  if (tile <= 2) return launch_tile<2>(a, block, tile, s);
+  if (tile <= 4) return launch_tile<4>(a, block, tile, s);
+  if (tile <= 8) return launch_tile<8>(a, block, tile, s);
+  if (tile <= 16) return launch_tile<16>(a, block, tile, s);
+  return launch_tile<32>(a, block, tile, s);
+}
+
+cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block, int64_t chunk,
+                                            cudaStream_t s, int64_t *launches) {
+  // Zero fill of the flattened output, then the atomic schedule.
+  cudaError_t e = launch_fill_zero(a.C, a.rows * a.n_rhs, block, s, launches);
+  if (e != cudaSuccess) return e;
+  const int64_t workers = ceil_div(a.nnz * a.n_rhs, chunk);
+  const unsigned grid = (unsigned)max1(ceil_div(workers, block));
+  spmm_thread_per_position_kernel<<<grid, block, 0, s>>>(a.rows, a.nnz, a.n_rhs, chunk, a.row_ptr,
+                                                         a.col_idx, a.val, a.B, a.C);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+}  // namespace swb

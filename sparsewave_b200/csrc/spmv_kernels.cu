@@ -1,0 +1,560 @@
+// CSR SpMV kernels for sm_100a: the three row mappings and the two position
+// mappings of sparsewave.spmv.  A reference "wave" (Wave32) is a CUDA warp.
+//
+// Arithmetic: products and sums are separate IEEE f32 operations
+// (__fmul_rn / __fadd_rn, never contracted to FMA), like the reference's
+// arith.mulf + arith.addf (SparseWaveToGPU.cpp:252-256).  thread-per-row adds
+// in position order, so it reproduces the CPU CSR loop bit for bit; the
+// cooperative mappings add the same products in a tree order.
+#include "swb_index.h"
+#include "swb_kernels.h"
+
+namespace swb {
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+__device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+
+// Streaming loads for data read once (col/val), cached loads for x.
+__device__ __forceinline__ int ld_stream(const int32_t *p) { return __ldcs(p); }
+__device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
+__device__ __forceinline__ int4 ld_stream(const int4 *p) { return __ldcs(p); }
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+
+// XOR butterfly, offsets 1,2,4,8,16: every lane ends with the warp sum
+// (buildWaveReduction, SparseGPUUtils.cpp:236-245).
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) v = add(v, __shfl_xor_sync(FULL, v, off));
+  return v;
+}
+
+// ---------------------------------------------------------------------------
+// zero fill (buildOutputInitialization, SparsePositionScheduling.cpp:31-47)
+// ---------------------------------------------------------------------------
+__global__ void fill_zero_kernel(float *__restrict__ y, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) y[i] = 0.0f;
+}
+
+// ---------------------------------------------------------------------------
+// thread-per-row (ThreadPerRowSpMVPattern, SparseWaveToGPU.cpp:216-274)
+// row = blockIdx * blockDim + threadIdx; sequential sum from 0.0f in position
+// order; plain store.
+// ---------------------------------------------------------------------------
+__global__ void spmv_thread_per_row_kernel(int64_t rows,
+                                           const int32_t *__restrict__ row_ptr,
+                                           const int32_t *__restrict__ col,
+                                           const float *__restrict__ val,
+                                           const float *__restrict__ x,
+                                           float *__restrict__ y) {
+  int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  int p = row_ptr[row];
+  const int end = row_ptr[row + 1];
+  float sum = 0.0f;
+  // Four independent (col, val, x) loads in flight, summed in position order.
+  for (; p + 4 <= end; p += 4) {
+    int c0 = ld_stream(col + p), c1 = ld_stream(col + p + 1);
+    int c2 = ld_stream(col + p + 2), c3 = ld_stream(col + p + 3);
+    float v0 = ld_stream(val + p), v1 = ld_stream(val + p + 1);
+    float v2 = ld_stream(val + p + 2), v3 = ld_stream(val + p + 3);
+    float x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
+    sum = add(sum, mul(v0, x0));
+    sum = add(sum, mul(v1, x1));
+    sum = add(sum, mul(v2, x2));
+    sum = add(sum, mul(v3, x3));
+  }
+  for (; p < end; ++p) sum = add(sum, mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))));
+  y[row] = sum;
+}
+
+// Partial sum of positions [start, end) taken by participant `who` of `count`
+// participants with stride `count`.  Rows of at least VEC_MIN positions use
+// 128-bit loads of the col/val streams: a scalar head up to the next 16-byte
+// boundary, int4/float4 groups strided over the participants, a scalar tail.
+constexpr int VEC_MIN = 128;
+
+__device__ __forceinline__ float strided_row_partial(int start, int end, int who, int count,
+                                                     const int32_t *__restrict__ col,
+                                                     const float *__restrict__ val,
+                                                     const float *__restrict__ x,
+                                                     bool vec_ok) {
+  float sum = 0.0f;
+  if (vec_ok && end - start >= VEC_MIN) {
+    const int a0 = (start + 3) & ~3;  // first 16-byte aligned position
+    int p = start + who;
+    if (p < a0) sum = add(sum, mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))));
+    const int g1 = end >> 2;
+    const int4 *col4 = reinterpret_cast<const int4 *>(col);
+    const float4 *val4 = reinterpret_cast<const float4 *>(val);
+    int g = (a0 >> 2) + who;
+    for (; g + count < g1; g += 2 * count) {
+      int4 ca = ld_stream(col4 + g), cb = ld_stream(col4 + g + count);
+      float4 va = ld_stream(val4 + g), vb = ld_stream(val4 + g + count);
+      float xa0 = __ldg(x + ca.x), xa1 = __ldg(x + ca.y), xa2 = __ldg(x + ca.z), xa3 = __ldg(x + ca.w);
+      float xb0 = __ldg(x + cb.x), xb1 = __ldg(x + cb.y), xb2 = __ldg(x + cb.z), xb3 = __ldg(x + cb.w);
+      sum = add(sum, mul(va.x, xa0)); sum = add(sum, mul(va.y, xa1));
+      sum = add(sum, mul(va.z, xa2)); sum = add(sum, mul(va.w, xa3));
+      sum = add(sum, mul(vb.x, xb0)); sum = add(sum, mul(vb.y, xb1));
+      sum = add(sum, mul(vb.z, xb2)); sum = add(sum, mul(vb.w, xb3));
+    }
+    for (; g < g1; g += count) {
+      int4 ca = ld_stream(col4 + g);
+      float4 va = ld_stream(val4 + g);
+      float xa0 = __ldg(x + ca.x), xa1 = __ldg(x + ca.y), xa2 = __ldg(x + ca.z), xa3 = __ldg(x + ca.w);
+      sum = add(sum, mul(va.x, xa0)); sum = add(sum, mul(va.y, xa1));
+      sum = add(sum, mul(va.z, xa2)); sum = add(sum, mul(va.w, xa3));
+    }
+    p = (g1 << 2) + who;
+    if (p < end) sum = add(sum, mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))));
+    return sum;
+  }
+  // Reference traversal: p = start + who, step count
+  // (buildStridedPositionRange, SparseGPUUtils.cpp:70-78), two loads in flight.
+  int p = start + who;
+  for (; p + count < end; p += 2 * count) {
+    int c0 = ld_stream(col + p), c1 = ld_stream(col + p + count);
+    float v0 = ld_stream(val + p), v1 = ld_stream(val + p + count);
+    float x0 = __ldg(x + c0), x1 = __ldg(x + c1);
+    sum = add(sum, mul(v0, x0));
+    sum = add(sum, mul(v1, x1));
+  }
+  if (p < end) sum = add(sum, mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))));
+  return sum;
+}
+
+// ---------------------------------------------------------------------------
+// wave-per-row (WavePerRowSpMVPattern, SparseWaveToGPU.cpp:276-354)
+// row = blockIdx * (blockDim/32) + threadIdx/32; lane-strided positions;
+// butterfly; lane 0 stores.
+// ---------------------------------------------------------------------------
+__global__ void spmv_wave_per_row_kernel(int64_t rows, const int32_t *__restrict__ row_ptr,
+                                         const int32_t *__restrict__ col,
+                                         const float *__restrict__ val,
+                                         const float *__restrict__ x, float *__restrict__ y,
+                                         bool vec_ok) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  float sum = strided_row_partial(start, end, lane, 32, col, val, x, vec_ok);
+  sum = warp_sum(sum);
+  if (lane == 0) y[row] = sum;
+}
+
+// ---------------------------------------------------------------------------
+// block-per-row (BlockPerRowSpMVPattern, SparseWaveToGPU.cpp:356-487)
+// row = blockIdx; thread-strided positions; warp butterfly -> shared
+// wave_sums[blockDim/32] -> barrier -> warp 0 butterfly over the partials ->
+// lane 0 stores.
+// ---------------------------------------------------------------------------
+__global__ void spmv_block_per_row_kernel(int64_t rows, const int32_t *__restrict__ row_ptr,
+                                          const int32_t *__restrict__ col,
+                                          const float *__restrict__ val,
+                                          const float *__restrict__ x, float *__restrict__ y,
+                                          bool vec_ok) {
+  __shared__ float wave_sums[32];
+  const int64_t row = blockIdx.x;
+  if (row >= rows) return;  // uniform for the block
+  const int lane = threadIdx.x & 31, wave = threadIdx.x >> 5;
+  const int waves = blockDim.x >> 5;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  float sum = strided_row_partial(start, end, threadIdx.x, blockDim.x, col, val, x, vec_ok);
+  sum = warp_sum(sum);
+  if (lane == 0) wave_sums[wave] = sum;
+  __syncthreads();
+  if (wave == 0) {
+    float v = lane < waves ? wave_sums[lane] : 0.0f;
+    v = warp_sum(v);
+    if (lane == 0) y[row] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// thread-per-position (ThreadPositionReducePattern and
+// ThreadSegmentedPositionReducePattern, SparsePositionScheduling.cpp:135-316)
+// worker = blockIdx * blockDim + threadIdx owns positions
+// [worker*chunk, min(nnz, (worker+1)*chunk)).  The row of the first position
+// comes from the upper-bound search; later rows by advancing over row
+// boundaries (buildNextCSRRowState, :108-133), which yields the same row the
+// per-position search would.  atomic: one atomicAdd per position.  segmented:
+// one atomicAdd per row change plus one at the chunk end.
+// ---------------------------------------------------------------------------
+template <bool SEGMENTED, bool TRACE>
+__global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64_t chunk,
+                                                const int32_t *__restrict__ row_ptr,
+                                                const int32_t *__restrict__ col,
+                                                const float *__restrict__ val,
+                                                const float *__restrict__ x,
+                                                float *__restrict__ y, PositionTrace trace) {
+  const int64_t worker = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t begin, end;
+  chunk_bounds(0, nnz, worker, chunk, begin, end);
+  if (begin >= end) return;
+  int64_t row = row_at_position(row_ptr, rows + 1, begin);
+  int64_t next = row_ptr[row + 1];
+  float acc = 0.0f;
+  int64_t acc_row = row;
+  for (int64_t p = begin; p < end; ++p) {
+    while (next <= p) {
+      ++row;
+      next = row_ptr[row + 1];
+    }
+    float prod = mul(ld_stream(val + p), __ldg(x + ld_stream(col + p)));
+    if (TRACE) {
+      trace.row_of_position[p] = (int32_t)row;
+      trace.worker_of_position[p] = (int32_t)worker;
+    }
+    if (SEGMENTED) {
+      if (row != acc_row) {
+        atomicAdd(y + acc_row, acc);
+        if (TRACE) trace.segment_end[p - 1] = 1;
+        acc = prod;
+        acc_row = row;
+      } else {
+        acc = (p == begin) ? prod : add(acc, prod);
+      }
+    } else {
+      atomicAdd(y + row, prod);
+      if (TRACE) trace.segment_end[p] = 1;
+    }
+  }
+  if (SEGMENTED) {
+    atomicAdd(y + acc_row, acc);
+    if (TRACE) trace.segment_end[end - 1] = 1;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// wave-per-position (WavePositionReducePattern, SparsePositionScheduling.cpp:
+// 318-403; segmented scan buildWavePrefixSegmentedReduction,
+// SparseGPUUtils.cpp:247-292).
+//
+// Reference schedule: W = max(ceil(nnz/B),1) * (B/32) waves; wave w owns
+// partition(0, nnz, w, W), at most 32 positions, lane = position - begin; a
+// segmented inclusive scan keyed on the row sums each row segment and the
+// segment-end lane issues one atomicAdd.
+//
+// Here one warp walks `batch` consecutive wave partitions (a contiguous span
+// of positions).  Rows are recovered once per tile of TILE_WAVES partitions:
+// one warp-cooperative 32-ary upper-bound search at the span start, then the
+// row offsets that follow are streamed with coalesced loads and each offset
+// that falls inside the tile marks its position in shared memory; a prefix
+// maximum turns the marks into the row of every position (the last row that
+// starts at or before it, so empty rows are skipped like the reference's
+// search does).  Inside a partition the reduction is the reference's:
+// segment heads from the row keys, a 5-step shuffle-up inclusive scan, one
+// atomicAdd per segment end.  The last, still open segment of a partition is
+// carried in registers into the next partition of the same warp and flushed
+// when its row ends or the span ends; with batch == 1 this is exactly one
+// atomicAdd per (partition, row) segment, the reference's count.
+// ---------------------------------------------------------------------------
+constexpr int TILE_WAVES = 8;
+constexpr int TILE_POS = TILE_WAVES * 32;
+
+// Smallest idx in [1, len) with row_ptr[idx] > pos, minus one; all lanes of the
+// warp take part and get the result.
+__device__ __forceinline__ int warp_row_search(const int32_t *__restrict__ row_ptr, int len,
+                                               int pos, int lane) {
+  int lo = 1, hi = len;
+  while (lo < hi) {
+    const int n = hi - lo;
+    const int step = (n + 31) >> 5;
+    const int64_t idx = (int64_t)lo + (int64_t)(lane + 1) * step - 1;
+    bool gt = true;
+    if (idx < hi) gt = __ldg(row_ptr + idx) > pos;
+    const unsigned m = __ballot_sync(FULL, gt);
+    if (m == 0) {
+      lo = hi;
+      break;
+    }
+    const int f = __ffs(m) - 1;
+    const int64_t nlo = (int64_t)lo + (int64_t)f * step;
+    int64_t nhi = nlo + step - 1;
+    if (nhi > hi) nhi = hi;
+    lo = (int)nlo;
+    hi = (int)nhi;
+  }
+  return lo - 1;
+}
+
+template <bool TRACE>
+__global__ void spmv_wave_per_position_kernel(int64_t rows, int64_t nnz, int64_t wave_count,
+                                              int64_t batch, const int32_t *__restrict__ row_ptr,
+                                              const int32_t *__restrict__ col,
+                                              const float *__restrict__ val,
+                                              const float *__restrict__ x, float *__restrict__ y,
+                                              PositionTrace trace) {
+  extern __shared__ int smem_rows[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int wpb = blockDim.x >> 5;
+  int *rowof = smem_rows + warp * TILE_POS;
+
+  const int64_t span_id = (int64_t)blockIdx.x * wpb + warp;
+  const int64_t w0 = span_id * batch;
+  if (w0 >= wave_count) return;
+  const int64_t w1 = (w0 + batch < wave_count) ? w0 + batch : wave_count;
+  const int64_t base = nnz / wave_count, rem = nnz % wave_count;
+  auto wave_begin = [&](int64_t w) { return w * base + (w < rem ? w : rem); };
+  const int64_t span_begin = wave_begin(w0), span_end = wave_begin(w1);
+  if (span_begin >= span_end) return;
+
+  // Row of the first position of the span.
+  int R = warp_row_search(row_ptr, (int)rows + 1, (int)span_begin, lane);
+
+  int carry_row = -1;   // row of the open segment, -1 if none
+  float acc = 0.0f;     // per-lane partial of the open segment
+  int64_t carry_last = span_begin - 1;  // last position folded into the carry
+
+  for (int64_t wt = w0; wt < w1; wt += TILE_WAVES) {
+    const int64_t wte = (wt + TILE_WAVES < w1) ? wt + TILE_WAVES : w1;
+    const int tile_begin = (int)wave_begin(wt), tile_end = (int)wave_begin(wte);
+    const int n = tile_end - tile_begin;
+    if (n <= 0) continue;
+
+    // 1. Issue the col/val loads of every partition of the tile.
+    int c[TILE_WAVES];
+    float v[TILE_WAVES];
+    int pos[TILE_WAVES];
+    bool act[TILE_WAVES];
+#pragma unroll
+    for (int j = 0; j < TILE_WAVES; ++j) {
+      const int64_t w = wt + j;
+      int b = tile_end, e = tile_end;
+      if (w < wte) {
+        b = (int)wave_begin(w);
+        e = (int)wave_begin(w + 1);
+      }
+      pos[j] = b + lane;
+      act[j] = pos[j] < e;
+      c[j] = 0;
+      v[j] = 0.0f;
+      if (act[j]) {
+        c[j] = ld_stream(col + pos[j]);
+        v[j] = ld_stream(val + pos[j]);
+      }
+    }
+
+    // 2. Row of every position of the tile.
+    __syncwarp();  // the previous tile's reads are done
+#pragma unroll
+    for (int i = 0; i < TILE_POS / 32; ++i) rowof[i * 32 + lane] = (i == 0 && lane == 0) ? R : -1;
+    __syncwarp();
+    bool any_boundary = false;
+    for (int64_t r0 = (int64_t)R + 1;; r0 += 32) {
+      const int64_t r = r0 + lane;
+      int b = 0x7fffffff;
+      if (r <= rows) b = __ldg(row_ptr + r);
+      const bool inside = b < tile_end;
+      if (inside) atomicMax(&rowof[b - tile_begin], (int)r);
+      const unsigned m = __ballot_sync(FULL, inside);
+      any_boundary |= (m != 0);
+      if (m != FULL) break;
+    }
+    __syncwarp();
+    if (any_boundary) {
+      // Inclusive prefix maximum over the tile, TILE_POS/32 entries per lane.
+      constexpr int PER = TILE_POS / 32;
+      int loc[PER];
+      int run = -1;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        run = max(run, rowof[lane * PER + i]);
+        loc[i] = run;
+      }
+      int incl = run;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        int t = __shfl_up_sync(FULL, incl, off);
+        if (lane >= off) incl = max(incl, t);
+      }
+      int excl = __shfl_up_sync(FULL, incl, 1);
+      if (lane == 0) excl = -1;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < PER; ++i) rowof[lane * PER + i] = max(loc[i], excl);
+      __syncwarp();
+      R = rowof[n - 1];
+    }
+
+    // 3. Gathers of x.
+    float prod[TILE_WAVES];
+#pragma unroll
+    for (int j = 0; j < TILE_WAVES; ++j) {
+      float xv = act[j] ? __ldg(x + c[j]) : 0.0f;
+      prod[j] = mul(v[j], xv);
+    }
+
+    // 4. Reduce partition by partition.
+#pragma unroll
+    for (int j = 0; j < TILE_WAVES; ++j) {
+      const unsigned amask = __ballot_sync(FULL, act[j]);
+      if (amask == 0) continue;  // uniform
+      const int idx = pos[j] - tile_begin;
+      const int row = act[j] ? (any_boundary ? rowof[idx] : R) : -2;
+      if (TRACE && act[j]) {
+        trace.row_of_position[pos[j]] = row;
+        trace.worker_of_position[pos[j]] = (int32_t)(wt + j);
+      }
+      const int nact = __popc(amask);  // active lanes form a prefix
+      const bool same = __all_sync(FULL, !act[j] || row == carry_row);
+      if (same) {
+        acc = add(acc, prod[j]);
+        carry_last = pos[0 + j] - lane + nact - 1;
+        continue;
+      }
+      // Close or merge the carried segment.
+      float val_j = prod[j];
+      const int first_row = __shfl_sync(FULL, row, 0);
+      if (carry_row >= 0) {
+        const float total = warp_sum(acc);
+        if (first_row == carry_row) {
+          if (lane == 0) val_j = add(total, val_j);
+        } else if (lane == 0) {
+          atomicAdd(y + carry_row, total);
+          if (TRACE) trace.segment_end[carry_last] = 1;
+        }
+      }
+      // Segment heads: lane 0, a row change, or an inactive lane.
+      const int prev_row = __shfl_up_sync(FULL, row, 1);
+      const bool head = (lane == 0) || (row != prev_row) || !act[j];
+      const unsigned hmask = __ballot_sync(FULL, head);
+      const unsigned le = (lane == 31) ? FULL : ((1u << (lane + 1)) - 1u);
+      const int dist = lane - (31 - __clz(hmask & le));
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float t = __shfl_up_sync(FULL, val_j, off);
+        if (off <= dist) val_j = add(val_j, t);
+      }
+      const bool next_head = (lane == 31) || ((hmask >> (lane + 1)) & 1u);
+      const bool last_active = (lane == nact - 1);
+      if (act[j] && next_head && !last_active) {
+        atomicAdd(y + row, val_j);
+        if (TRACE) trace.segment_end[pos[j]] = 1;
+      }
+      // The segment of the last active lane stays open.
+      carry_row = __shfl_sync(FULL, row, nact - 1);
+      acc = last_active ? val_j : 0.0f;
+      carry_last = pos[j] - lane + nact - 1;
+    }
+  }
+  if (carry_row >= 0) {
+    const float total = warp_sum(acc);
+    if (lane == 0) {
+      atomicAdd(y + carry_row, total);
+      if (TRACE) trace.segment_end[carry_last] = 1;
+    }
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline unsigned grid_of(int64_t blocks) { return (unsigned)max1(blocks); }
+
+}  // namespace
+
+cudaError_t launch_fill_zero(float *y, int64_t n, int block, cudaStream_t s, int64_t *launches) {
+  // Thread mapping over len(y) (SparsePositionScheduling.cpp:31-47); the grid
+  // is capped and threads stride, which stores the same zeros.
+  int64_t blocks = max1(ceil_div(n, block));
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  fill_zero_kernel<<<(unsigned)blocks, block, 0, s>>>(y, n);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_spmv_thread_per_row(const CsrSpmvArgs &a, int block, cudaStream_t s,
+                                       int64_t *launches) {
+  spmv_thread_per_row_kernel<<<grid_of(ceil_div(a.rows, block)), block, 0, s>>>(
+      a.rows, a.row_ptr, a.col_idx, a.val, a.x, a.y);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_spmv_wave_per_row(const CsrSpmvArgs &a, int block, cudaStream_t s,
+                                     int64_t *launches) {
+  const bool vec_ok = aligned16(a.col_idx) && aligned16(a.val);
+  spmv_wave_per_row_kernel<<<grid_of(ceil_div(a.rows, block / 32)), block, 0, s>>>(
+      a.rows, a.row_ptr, a.col_idx, a.val, a.x, a.y, vec_ok);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_spmv_block_per_row(const CsrSpmvArgs &a, int block, cudaStream_t s,
+                                      int64_t *launches) {
+  const bool vec_ok = aligned16(a.col_idx) && aligned16(a.val);
+  spmv_block_per_row_kernel<<<grid_of(a.rows), block, 0, s>>>(a.rows, a.row_ptr, a.col_idx,
+                                                               a.val, a.x, a.y, vec_ok);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_spmv_thread_per_position(const CsrSpmvArgs &a, int block, int64_t chunk,
+                                            bool segmented, const PositionTrace &trace,
+                                            cudaStream_t s, int64_t *launches) {
+  cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
+  if (e != cudaSuccess) return e;
+  const int64_t workers = ceil_div(a.nnz, chunk);
+  const unsigned grid = grid_of(ceil_div(workers, block));
+  if (trace.enabled()) {
+    if (segmented)
+      spmv_thread_per_position_kernel<true, true><<<grid, block, 0, s>>>(
+          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+    else
+      spmv_thread_per_position_kernel<false, true><<<grid, block, 0, s>>>(
+          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+  } else {
+    if (segmented)
+      spmv_thread_per_position_kernel<true, false><<<grid, block, 0, s>>>(
+          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+    else
+      spmv_thread_per_position_kernel<false, false><<<grid, block, 0, s>>>(
+          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+  }
+  ++*launches;
+  return cudaGetLastError();
+}
+
+int64_t wave_per_position_auto_batch(int64_t nnz, int block, const DeviceInfo &dev) {
+  // Enough warps to fill every SM several times over, spans long enough that
+  // the one search per span is amortised; whole tiles when the span is long.
+  const int64_t waves = wave_position_wave_count(nnz, block);
+  const int64_t target_warps = (int64_t)dev.sm_count * 64 * 4;
+  int64_t batch = waves / target_warps;
+  if (batch < 1) batch = 1;
+  if (batch > 64) batch = 64;
+  if (batch > TILE_WAVES) batch -= batch % TILE_WAVES;
+  return batch;
+}
+
+int64_t wave_per_position_physical_grid(int64_t nnz, int block, int64_t batch) {
+  const int64_t waves = wave_position_wave_count(nnz, block);
+  const int64_t spans = ceil_div(waves, batch);
+  return max1(ceil_div(spans, block / 32));
+}
+
+cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64_t batch,
+                                          const PositionTrace &trace, cudaStream_t s,
+                                          int64_t *launches, int64_t *physical_grid) {
+  cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
+  if (e != cudaSuccess) return e;
+  const int64_t waves = wave_position_wave_count(a.nnz, block);
+  const int64_t grid = wave_per_position_physical_grid(a.nnz, block, batch);
+  if (physical_grid) *physical_grid = grid;
+  const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
+  if (trace.enabled())
+    spmv_wave_per_position_kernel<true><<<(unsigned)grid, block, smem, s>>>(
+        a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+  else
+    spmv_wave_per_position_kernel<false><<<(unsigned)grid, block, smem, s>>>(
+        a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+}  // namespace swb

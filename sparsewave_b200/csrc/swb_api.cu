@@ -1,0 +1,880 @@
+// C ABI of libsparsewave_b200.so: context, option parsing and validation with
+// the reference's diagnostics, operand checks, dispatch to the kernels.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/sparsewave_b200.h"
+#include "swb_index.h"
+#include "swb_kernels.h"
+
+struct swb_context {
+  int device = 0;
+  swb::DeviceInfo dev;
+  std::string error;
+  int64_t launches = 0;
+  // Device workspace of the *_host entry points: one allocation, grown on
+  // demand, carved by a bump pointer per call.
+  char *workspace = nullptr;
+  size_t workspace_bytes = 0;
+  size_t workspace_used = 0;
+  cudaStream_t host_stream = nullptr;
+  int *status_flag = nullptr;  // device int for kernels with bounded waits
+};
+
+namespace {
+
+thread_local std::string g_thread_error;
+
+int fail(swb_context *ctx, int status, const char *fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx)
+    ctx->error = buf;
+  else
+    g_thread_error = buf;
+  return status;
+}
+
+int cuda_fail(swb_context *ctx, cudaError_t e, const char *what) {
+  return fail(ctx, SWB_ERR_CUDA, "CUDA error in %s: %s", what, cudaGetErrorString(e));
+}
+
+const char *spmv_mapping_name(int m) {
+  switch (m) {
+    case SWB_THREAD_PER_ROW: return "thread-per-row";
+    case SWB_THREAD_PER_POSITION: return "thread-per-position";
+    case SWB_WAVE_PER_POSITION: return "wave-per-position";
+    case SWB_WAVE_PER_ROW: return "wave-per-row";
+    case SWB_BLOCK_PER_ROW: return "block-per-row";
+  }
+  return nullptr;
+}
+
+bool is_position_mapping(int m) {
+  return m == SWB_THREAD_PER_POSITION || m == SWB_WAVE_PER_POSITION;
+}
+
+// Keys of operators outside this library: parsed, range-checked with the
+// reference's message (SparseWaveToGPU.cpp:1315-1346), otherwise unused.
+struct ForeignBlockSize {
+  const char *key;
+  const char *label;
+};
+const ForeignBlockSize kForeign[] = {
+    {"sddmm-block-size", "SDDMM block size"},
+    {"row-reduction-block-size", "CSR row-reduction block size"},
+    {"rowwise-map-block-size", "CSR row-wise map block size"},
+    {"elementwise-block-size", "elementwise block size"},
+};
+
+bool parse_int(const std::string &s, int64_t &out) {
+  if (s.empty()) return false;
+  char *end = nullptr;
+  long long v = strtoll(s.c_str(), &end, 10);
+  if (*end != '\0') return false;
+  out = v;
+  return true;
+}
+
+constexpr int64_t kI32Max = 2147483647LL;
+
+int check_ctx(swb_context *ctx) {
+  if (!ctx) return fail(nullptr, SWB_ERR_INVALID_ARGUMENT, "context is NULL");
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaSetDevice");
+  return SWB_OK;
+}
+
+int check_csr_sizes(swb_context *ctx, const char *op, int64_t rows, int64_t cols, int64_t nnz) {
+  if (rows < 0 || cols < 0 || nnz < 0)
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "%s: rows, cols and nnz must be non-negative", op);
+  // i32 row offsets and column indices (benchmark/run_spmv_benchmark.py:581-600).
+  if (rows >= kI32Max || cols > kI32Max || nnz > kI32Max)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "%s: matrix rows and NNZ must fit in the i32 CSR type", op);
+  return SWB_OK;
+}
+
+// Workspace -----------------------------------------------------------------
+int workspace_reserve(swb_context *ctx, size_t bytes) {
+  ctx->workspace_used = 0;
+  if (bytes <= ctx->workspace_bytes) return SWB_OK;
+  if (ctx->workspace) {
+    cudaFree(ctx->workspace);
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+  }
+  cudaError_t e = cudaMalloc(&ctx->workspace, bytes);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMalloc(workspace)");
+  ctx->workspace_bytes = bytes;
+  return SWB_OK;
+}
+
+size_t pad256(size_t b) { return (b + 255) & ~(size_t)255; }
+
+template <typename T>
+T *workspace_take(swb_context *ctx, size_t count) {
+  T *p = reinterpret_cast<T *>(ctx->workspace + ctx->workspace_used);
+  ctx->workspace_used += pad256(count * sizeof(T));
+  return p;
+}
+
+int ensure_host_stream(swb_context *ctx) {
+  if (ctx->host_stream) return SWB_OK;
+  cudaError_t e = cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamCreate");
+  return SWB_OK;
+}
+
+#define SWB_CUDA(ctx, call)                                   \
+  do {                                                        \
+    cudaError_t e__ = (call);                                 \
+    if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+const char *swb_version(void) { return "sparsewave_b200 0.1 (sm_100a)"; }
+
+int swb_create(swb_context **out_ctx, int device_ordinal) {
+  if (!out_ctx) return fail(nullptr, SWB_ERR_INVALID_ARGUMENT, "out_ctx is NULL");
+  *out_ctx = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDeviceCount");
+  if (device_ordinal < 0 || device_ordinal >= count)
+    return fail(nullptr, SWB_ERR_CUDA, "CUDA device %d is not available (%d devices)", device_ordinal, count);
+  e = cudaSetDevice(device_ordinal);
+  if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+  swb_context *ctx = new swb_context();
+  ctx->device = device_ordinal;
+  cudaDeviceGetAttribute(&ctx->dev.sm_count, cudaDevAttrMultiProcessorCount, device_ordinal);
+  cudaDeviceGetAttribute(&ctx->dev.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_ordinal);
+  *out_ctx = ctx;
+  return SWB_OK;
+}
+
+void swb_destroy(swb_context *ctx) {
+  if (!ctx) return;
+  cudaSetDevice(ctx->device);
+  if (ctx->workspace) cudaFree(ctx->workspace);
+  if (ctx->status_flag) cudaFree(ctx->status_flag);
+  if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+  delete ctx;
+}
+
+const char *swb_last_error(const swb_context *ctx) {
+  return ctx ? ctx->error.c_str() : g_thread_error.c_str();
+}
+
+int64_t swb_kernel_launch_count(const swb_context *ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- options ---------------------------------------------------------------
+
+void swb_options_default(swb_options *o) {
+  if (!o) return;
+  memset(o, 0, sizeof *o);
+  o->mapping = SWB_THREAD_PER_ROW;
+  o->position_reduction = SWB_REDUCTION_ATOMIC;
+  o->spmm_mapping = SWB_THREAD_PER_OUTPUT;
+  o->block_size = 256;
+  o->wave_size = 32;
+  o->position_block_size = 256;
+  o->position_chunk_size = 1;
+  o->spmm_block_size = 256;
+  o->spmm_tile_size = 4;
+  o->spmm_position_chunk_size = 1;
+  o->wave_position_batch = 0;
+}
+
+int swb_options_parse(swb_context *ctx, swb_options *o, const char *text) {
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
+  if (!text) return SWB_OK;
+  std::string s(text);
+  size_t i = 0;
+  while (i < s.size()) {
+    while (i < s.size() && (s[i] == ' ' || s[i] == ',' || s[i] == '\t' || s[i] == '\n')) ++i;
+    if (i >= s.size()) break;
+    size_t j = i;
+    while (j < s.size() && s[j] != ' ' && s[j] != ',' && s[j] != '\t' && s[j] != '\n') ++j;
+    std::string tok = s.substr(i, j - i);
+    i = j;
+    size_t eq = tok.find('=');
+    if (eq == std::string::npos)
+      return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "expected key=value, but got '%s'", tok.c_str());
+    std::string key = tok.substr(0, eq), value = tok.substr(eq + 1);
+    int64_t n = 0;
+    auto want_int = [&](int64_t &dst) -> int {
+      if (!parse_int(value, n))
+        return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "option '%s' expects an integer, but got '%s'", key.c_str(), value.c_str());
+      dst = n;
+      return SWB_OK;
+    };
+    int st = SWB_OK;
+    if (key == "mapping" || key == "spmv-mapping") {
+      if (value == "thread-per-row") o->mapping = SWB_THREAD_PER_ROW;
+      else if (value == "wave-per-row") o->mapping = SWB_WAVE_PER_ROW;
+      else if (value == "block-per-row") o->mapping = SWB_BLOCK_PER_ROW;
+      else if (value == "thread-per-position" || (key == "mapping" && value == "thread")) o->mapping = SWB_THREAD_PER_POSITION;
+      else if (value == "wave-per-position" || (key == "mapping" && value == "wave")) o->mapping = SWB_WAVE_PER_POSITION;
+      else if (key == "mapping" && value == "block")
+        // schedule-sparsewave-position mapping (SparsePositionScheduling.cpp:412-417)
+        return fail(ctx, SWB_ERR_INVALID_OPTION, "unsupported position mapping '%s'; expected 'thread' or 'wave'", value.c_str());
+      else
+        return fail(ctx, SWB_ERR_INVALID_OPTION,
+                    "unsupported SpMV mapping strategy '%s'; expected 'thread-per-row', 'wave-per-row', or 'block-per-row'",
+                    value.c_str());
+    } else if (key == "spmm-mapping") {
+      if (value == "thread-per-output") o->spmm_mapping = SWB_THREAD_PER_OUTPUT;
+      else if (value == "wave-per-row-tile") o->spmm_mapping = SWB_WAVE_PER_ROW_TILE;
+      else if (value == "thread-per-position") o->spmm_mapping = SWB_SPMM_THREAD_PER_POSITION;
+      else
+        return fail(ctx, SWB_ERR_INVALID_OPTION,
+                    "unsupported SpMM mapping strategy '%s'; expected 'thread-per-output' or 'wave-per-row-tile'",
+                    value.c_str());
+    } else if (key == "thread-reduction" || key == "spmv-position-reduction") {
+      if (value == "atomic") o->position_reduction = SWB_REDUCTION_ATOMIC;
+      else if (value == "segmented") o->position_reduction = SWB_REDUCTION_SEGMENTED;
+      else
+        return fail(ctx, SWB_ERR_INVALID_OPTION,
+                    "unsupported thread position reduction '%s'; expected 'atomic' or 'segmented'", value.c_str());
+    } else if (key == "block-size" || key == "spmv-block-size") st = want_int(o->block_size);
+    else if (key == "wave-size" || key == "wavefront-size") st = want_int(o->wave_size);
+    else if (key == "position-block-size") st = want_int(o->position_block_size);
+    else if (key == "thread-chunk-size" || key == "spmv-position-chunk-size") st = want_int(o->position_chunk_size);
+    else if (key == "spmm-block-size") st = want_int(o->spmm_block_size);
+    else if (key == "spmm-tile-size") st = want_int(o->spmm_tile_size);
+    else if (key == "spmm-position-chunk-size") st = want_int(o->spmm_position_chunk_size);
+    else if (key == "wave-position-batch") st = want_int(o->wave_position_batch);
+    else {
+      bool foreign = false;
+      for (const ForeignBlockSize &f : kForeign) {
+        if (key == f.key) {
+          foreign = true;
+          int64_t v = 0;
+          st = want_int(v);
+          if (st == SWB_OK && (v < 1 || v > 1024))
+            return fail(ctx, SWB_ERR_INVALID_OPTION, "%s must be between 1 and 1024, but got %lld", f.label, (long long)v);
+        }
+      }
+      if (!foreign) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "unknown option '%s'", key.c_str());
+    }
+    if (st != SWB_OK) return st;
+  }
+  return SWB_OK;
+}
+
+int swb_options_validate(swb_context *ctx, const swb_options *o) {
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
+  const char *name = spmv_mapping_name(o->mapping);
+  if (!name)
+    return fail(ctx, SWB_ERR_INVALID_OPTION,
+                "unsupported SpMV mapping strategy '%d'; expected 'thread-per-row', 'wave-per-row', or 'block-per-row'",
+                o->mapping);
+  if (o->spmm_mapping < SWB_THREAD_PER_OUTPUT || o->spmm_mapping > SWB_SPMM_THREAD_PER_POSITION)
+    return fail(ctx, SWB_ERR_INVALID_OPTION,
+                "unsupported SpMM mapping strategy '%d'; expected 'thread-per-output' or 'wave-per-row-tile'",
+                o->spmm_mapping);
+  if (o->position_reduction != SWB_REDUCTION_ATOMIC && o->position_reduction != SWB_REDUCTION_SEGMENTED)
+    return fail(ctx, SWB_ERR_INVALID_OPTION,
+                "unsupported thread position reduction '%d'; expected 'atomic' or 'segmented'", o->position_reduction);
+
+  // schedule-sparsewave-position (SparsePositionScheduling.cpp:411-465); the
+  // pipeline feeds it spmv-block-size (Pipelines.cpp:249).
+  if (is_position_mapping(o->mapping)) {
+    const bool wave = o->mapping == SWB_WAVE_PER_POSITION;
+    if (o->block_size < 1 || o->block_size > 1024)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "position block size must be between 1 and 1024, but got %lld", (long long)o->block_size);
+    if (wave && o->wave_size != 32)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "wave position mapping currently requires Wave32, but got %lld", (long long)o->wave_size);
+    if (wave && o->block_size % o->wave_size != 0)
+      return fail(ctx, SWB_ERR_INVALID_OPTION,
+                  "wave position mapping requires the block size to be a multiple of %lld, but got %lld",
+                  (long long)o->wave_size, (long long)o->block_size);
+    if (o->position_chunk_size < 1)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "thread position chunk size must be positive, but got %lld", (long long)o->position_chunk_size);
+    if (wave && o->position_chunk_size != 1)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "thread position chunk size applies only to thread mapping");
+    if (wave && o->position_reduction != SWB_REDUCTION_ATOMIC)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "thread position reduction applies only to thread mapping");
+    if (o->wave_position_batch < 0)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "wave position batch must be non-negative, but got %lld", (long long)o->wave_position_batch);
+  }
+  if (o->spmm_mapping == SWB_SPMM_THREAD_PER_POSITION) {
+    if (o->spmm_block_size < 1 || o->spmm_block_size > 1024)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "position block size must be between 1 and 1024, but got %lld", (long long)o->spmm_block_size);
+    if (o->spmm_position_chunk_size < 1)
+      return fail(ctx, SWB_ERR_INVALID_OPTION, "thread position chunk size must be positive, but got %lld", (long long)o->spmm_position_chunk_size);
+  }
+
+  // convert-sparsewave-to-gpu (SparseWaveToGPU.cpp:1282-1372).
+  if (o->block_size < 1 || o->block_size > 1024)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "SpMV block size must be between 1 and 1024, but got %lld", (long long)o->block_size);
+  if (o->position_block_size < 1 || o->position_block_size > 1024)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "position-parallel block size must be between 1 and 1024, but got %lld", (long long)o->position_block_size);
+  if (o->spmm_block_size < 1 || o->spmm_block_size > 1024)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "SpMM block size must be between 1 and 1024, but got %lld", (long long)o->spmm_block_size);
+  if (o->spmm_tile_size < 1 || o->spmm_tile_size > 32)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "SpMM tile size must be between 1 and 32, but got %lld", (long long)o->spmm_tile_size);
+  if (o->spmm_mapping == SWB_WAVE_PER_ROW_TILE && o->wave_size != 32)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "wave-per-row-tile currently requires Wave32, but got wave size %lld", (long long)o->wave_size);
+  if (o->spmm_mapping == SWB_WAVE_PER_ROW_TILE && o->spmm_block_size % o->wave_size != 0)
+    return fail(ctx, SWB_ERR_INVALID_OPTION,
+                "wave-per-row-tile requires the SpMM block size to be a multiple of %lld, but got %lld",
+                (long long)o->wave_size, (long long)o->spmm_block_size);
+  const bool cooperative = o->mapping == SWB_WAVE_PER_ROW || o->mapping == SWB_BLOCK_PER_ROW;
+  if (cooperative && o->wave_size != 32)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "%s currently requires Wave32, but got wave size %lld", name, (long long)o->wave_size);
+  if (cooperative && o->block_size % o->wave_size != 0)
+    return fail(ctx, SWB_ERR_INVALID_OPTION, "%s requires the SpMV block size to be a multiple of %lld, but got %lld",
+                name, (long long)o->wave_size, (long long)o->block_size);
+  return SWB_OK;
+}
+
+// ---- index helpers -----------------------------------------------------------
+
+void swb_partition(int64_t lower, int64_t upper, int64_t worker, int64_t count, int64_t *b, int64_t *e) {
+  int64_t bb, ee;
+  swb::partition(lower, upper, worker, count, bb, ee);
+  if (b) *b = bb;
+  if (e) *e = ee;
+}
+
+void swb_chunk_bounds(int64_t lower, int64_t upper, int64_t worker, int64_t factor, int64_t *b, int64_t *e) {
+  int64_t bb, ee;
+  swb::chunk_bounds(lower, upper, worker, factor, bb, ee);
+  if (b) *b = bb;
+  if (e) *e = ee;
+}
+
+int64_t swb_row_at_position(const int32_t *row_ptr, int64_t len, int64_t position) {
+  return swb::row_at_position(row_ptr, len, position);
+}
+
+int swb_launch_shape_query(swb_context *ctx, const swb_options *o, int64_t rows, int64_t nnz,
+                           int64_t n_rhs, swb_launch_shape *out) {
+  if (!out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "out is NULL");
+  int st = swb_options_validate(ctx, o);
+  if (st != SWB_OK) return st;
+  swb::DeviceInfo dev;
+  if (ctx) dev = ctx->dev;
+  swb_launch_shape r = {0, 0, 0, 1, 0};
+  using swb::ceil_div;
+  using swb::max1;
+  if (n_rhs == 0) {
+    const int64_t B = o->block_size;
+    r.logical_block = B;
+    switch (o->mapping) {
+      case SWB_THREAD_PER_ROW:
+        r.work_units = rows;
+        r.logical_grid = max1(ceil_div(rows, B));
+        r.physical_grid = r.logical_grid;
+        break;
+      case SWB_WAVE_PER_ROW:
+        r.work_units = rows;
+        r.logical_grid = max1(ceil_div(rows, B / 32));
+        r.physical_grid = r.logical_grid;
+        break;
+      case SWB_BLOCK_PER_ROW:
+        r.work_units = rows;
+        r.logical_grid = max1(rows);
+        r.physical_grid = r.logical_grid;
+        break;
+      case SWB_THREAD_PER_POSITION:
+        r.work_units = ceil_div(nnz, o->position_chunk_size);
+        r.logical_grid = max1(ceil_div(r.work_units, B));
+        r.physical_grid = r.logical_grid;
+        r.kernels = 2;
+        break;
+      case SWB_WAVE_PER_POSITION: {
+        r.work_units = swb::wave_position_wave_count(nnz, B);
+        r.logical_grid = max1(ceil_div(nnz, B));
+        int64_t batch = o->wave_position_batch > 0 ? o->wave_position_batch
+                                                   : swb::wave_per_position_auto_batch(nnz, (int)B, dev);
+        r.physical_grid = swb::wave_per_position_physical_grid(nnz, (int)B, batch);
+        r.kernels = 2;
+        break;
+      }
+    }
+  } else {
+    const int64_t B = o->spmm_block_size;
+    r.logical_block = B;
+    switch (o->spmm_mapping) {
+      case SWB_THREAD_PER_OUTPUT:
+        r.work_units = rows * n_rhs;
+        r.logical_grid = max1(ceil_div(r.work_units, B));
+        break;
+      case SWB_WAVE_PER_ROW_TILE:
+        r.work_units = rows * ceil_div(n_rhs, o->spmm_tile_size);
+        r.logical_grid = max1(ceil_div(r.work_units, B / 32));
+        break;
+      case SWB_SPMM_THREAD_PER_POSITION:
+        r.work_units = ceil_div(nnz * n_rhs, o->spmm_position_chunk_size);
+        r.logical_grid = max1(ceil_div(r.work_units, B));
+        r.kernels = 2;
+        break;
+    }
+    r.physical_grid = r.logical_grid;
+  }
+  *out = r;
+  return SWB_OK;
+}
+
+// ---- operators ----------------------------------------------------------------
+
+static int spmv_impl(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
+                     const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x,
+                     float *y, const swb::PositionTrace &trace, cudaStream_t stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = swb_options_validate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_csr_sizes(ctx, "spmv", rows, cols, nnz);
+  if (st != SWB_OK) return st;
+  if (!row_ptr || (nnz > 0 && (!col_idx || !val)) || (cols > 0 && !x) || (rows > 0 && !y))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL operand pointer");
+  if (trace.enabled() && !is_position_mapping(o->mapping))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "position trace requires a position mapping");
+  swb::CsrSpmvArgs a{rows, cols, nnz, row_ptr, col_idx, val, x, y};
+  const int B = (int)o->block_size;
+  cudaError_t e = cudaSuccess;
+  switch (o->mapping) {
+    case SWB_THREAD_PER_ROW: e = swb::launch_spmv_thread_per_row(a, B, stream, &ctx->launches); break;
+    case SWB_WAVE_PER_ROW: e = swb::launch_spmv_wave_per_row(a, B, stream, &ctx->launches); break;
+    case SWB_BLOCK_PER_ROW: e = swb::launch_spmv_block_per_row(a, B, stream, &ctx->launches); break;
+    case SWB_THREAD_PER_POSITION:
+      e = swb::launch_spmv_thread_per_position(a, B, o->position_chunk_size,
+                                               o->position_reduction == SWB_REDUCTION_SEGMENTED, trace,
+                                               stream, &ctx->launches);
+      break;
+    case SWB_WAVE_PER_POSITION: {
+      int64_t batch = o->wave_position_batch > 0 ? o->wave_position_batch
+                                                 : swb::wave_per_position_auto_batch(nnz, B, ctx->dev);
+      e = swb::launch_spmv_wave_per_position(a, B, batch, trace, stream, &ctx->launches, nullptr);
+      break;
+    }
+  }
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "spmv launch");
+  return SWB_OK;
+}
+
+int swb_spmv(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
+             const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x, float *y,
+             swb_stream stream) {
+  return spmv_impl(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, swb::PositionTrace(),
+                   static_cast<cudaStream_t>(stream));
+}
+
+int swb_spmv_position_trace(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
+                            const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x,
+                            float *y, int32_t *row_of_position, int32_t *worker_of_position,
+                            int32_t *segment_end, swb_stream stream) {
+  if (!ctx) return fail(nullptr, SWB_ERR_INVALID_ARGUMENT, "context is NULL");
+  if (nnz > 0 && (!row_of_position || !worker_of_position || !segment_end))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "position trace: NULL trace pointer");
+  swb::PositionTrace t;
+  t.row_of_position = row_of_position;
+  t.worker_of_position = worker_of_position;
+  t.segment_end = segment_end;
+  if (nnz > 0) {
+    int st = check_ctx(ctx);
+    if (st != SWB_OK) return st;
+    SWB_CUDA(ctx, cudaMemsetAsync(segment_end, 0, (size_t)nnz * sizeof(int32_t), static_cast<cudaStream_t>(stream)));
+  }
+  return spmv_impl(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, t, static_cast<cudaStream_t>(stream));
+}
+
+int swb_spmm(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz, int64_t n_rhs,
+             const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *B, float *C,
+             swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = swb_options_validate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_csr_sizes(ctx, "spmm", rows, cols, nnz);
+  if (st != SWB_OK) return st;
+  // The reference loaders require at least one right-hand-side column
+  // (SparseBenchmarkUtils.cpp:262-263).
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  if (!row_ptr || (nnz > 0 && (!col_idx || !val)) || (cols > 0 && !B) || (rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL operand pointer");
+  swb::CsrSpmmArgs a{rows, cols, nnz, n_rhs, row_ptr, col_idx, val, B, C};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int Bs = (int)o->spmm_block_size;
+  cudaError_t e = cudaSuccess;
+  switch (o->spmm_mapping) {
+    case SWB_THREAD_PER_OUTPUT: e = swb::launch_spmm_thread_per_output(a, Bs, s, &ctx->launches); break;
+    case SWB_WAVE_PER_ROW_TILE: e = swb::launch_spmm_wave_per_row_tile(a, Bs, (int)o->spmm_tile_size, s, &ctx->launches); break;
+    case SWB_SPMM_THREAD_PER_POSITION:
+      e = swb::launch_spmm_thread_per_position(a, Bs, o->spmm_position_chunk_size, s, &ctx->launches);
+      break;
+  }
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "spmm launch");
+  return SWB_OK;
+}
+
+static int check_bsr(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnzb, int64_t bs, int64_t n_rhs) {
+  if (rows < 0 || cols < 0 || nnzb < 0)
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: rows, cols and nnzb must be non-negative");
+  // verifyBSRStorage / BSRSpMMOp::verify (SparseWaveOps.cpp:144-207, 340-372)
+  if (bs <= 0) return fail(ctx, SWB_ERR_INVALID_SHAPE, "block size must be positive, but got %lld", (long long)bs);
+  if (rows % bs != 0)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "output rows must be divisible by block size, but got %lld and %lld", (long long)rows, (long long)bs);
+  if (cols % bs != 0)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "right-hand-side rows must be divisible by block size, but got %lld and %lld", (long long)cols, (long long)bs);
+  if (rows > kI32Max || cols > kI32Max || nnzb > kI32Max)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "BSR dimensions and NNZ blocks must fit in i32");
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "bsr_spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  return SWB_OK;
+}
+
+int swb_bsr_spmm_f32(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnzb,
+                     int64_t bs, int64_t n_rhs, const int32_t *brp, const int32_t *bci, const float *bv,
+                     const float *B, float *C, swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = swb_options_validate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_bsr(ctx, rows, cols, nnzb, bs, n_rhs);
+  if (st != SWB_OK) return st;
+  if (!brp || (nnzb > 0 && (!bci || !bv)) || (cols > 0 && !B) || (rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: NULL operand pointer");
+  swb::BsrSpmmArgs a{rows, cols, nnzb, bs, n_rhs, brp, bci, bv, B, C};
+  cudaError_t e = swb::launch_bsr_spmm_thread_per_output_f32(a, (int)o->spmm_block_size,
+                                                             static_cast<cudaStream_t>(stream), &ctx->launches);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "bsr_spmm launch");
+  return SWB_OK;
+}
+
+int swb_bsr_spmm_bf16(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnzb,
+                      int64_t bs, int64_t n_rhs, const int32_t *brp, const int32_t *bci, const uint16_t *bv,
+                      const uint16_t *B, uint16_t *C, swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = swb_options_validate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_bsr(ctx, rows, cols, nnzb, bs, n_rhs);
+  if (st != SWB_OK) return st;
+  if (!brp || (nnzb > 0 && (!bci || !bv)) || (cols > 0 && !B) || (rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: NULL operand pointer");
+  swb::BsrSpmmArgs a{rows, cols, nnzb, bs, n_rhs, brp, bci, bv, B, C};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = swb::launch_bsr_spmm_thread_per_output_bf16(a, (int)o->spmm_block_size, s, &ctx->launches);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "bsr_spmm launch");
+  return SWB_OK;
+}
+
+// ---- host-buffer entry points -----------------------------------------------------
+
+int swb_check_csr_host(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, const int32_t *row_ptr,
+                       const int32_t *col_idx) {
+  int st = check_csr_sizes(ctx, "csr", rows, cols, nnz);
+  if (st != SWB_OK) return st;
+  if (!row_ptr || (nnz > 0 && !col_idx)) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr: NULL operand pointer");
+  if (row_ptr[0] != 0) return fail(ctx, SWB_ERR_INVALID_DATA, "row offsets must start at 0, but got %d", row_ptr[0]);
+  for (int64_t r = 0; r < rows; ++r)
+    if (row_ptr[r + 1] < row_ptr[r])
+      return fail(ctx, SWB_ERR_INVALID_DATA, "row offsets must be non-decreasing, but row %lld has %d > %d",
+                  (long long)r, row_ptr[r], row_ptr[r + 1]);
+  if (row_ptr[rows] != nnz)
+    return fail(ctx, SWB_ERR_INVALID_DATA, "last row offset must equal NNZ, but got %d and %lld", row_ptr[rows], (long long)nnz);
+  for (int64_t p = 0; p < nnz; ++p)
+    if (col_idx[p] < 0 || col_idx[p] >= cols)
+      return fail(ctx, SWB_ERR_INVALID_DATA, "column index %d at position %lld is out of bounds for %lld columns",
+                  col_idx[p], (long long)p, (long long)cols);
+  return SWB_OK;
+}
+
+int swb_spmv_host(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
+                  const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x, float *y) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = check_csr_sizes(ctx, "spmv", rows, cols, nnz);
+  if (st != SWB_OK) return st;
+  if (!row_ptr || (nnz > 0 && (!col_idx || !val)) || (cols > 0 && !x) || (rows > 0 && !y))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  size_t need = pad256((rows + 1) * 4) + 2 * pad256(nnz * 4) + pad256(cols * 4) + pad256(rows * 4);
+  st = workspace_reserve(ctx, need);
+  if (st != SWB_OK) return st;
+  int32_t *d_rp = workspace_take<int32_t>(ctx, rows + 1);
+  int32_t *d_ci = workspace_take<int32_t>(ctx, nnz);
+  float *d_v = workspace_take<float>(ctx, nnz);
+  float *d_x = workspace_take<float>(ctx, cols);
+  float *d_y = workspace_take<float>(ctx, rows);
+  cudaStream_t s = ctx->host_stream;
+  SWB_CUDA(ctx, cudaMemcpyAsync(d_rp, row_ptr, (rows + 1) * 4, cudaMemcpyHostToDevice, s));
+  if (nnz > 0) {
+    SWB_CUDA(ctx, cudaMemcpyAsync(d_ci, col_idx, nnz * 4, cudaMemcpyHostToDevice, s));
+    SWB_CUDA(ctx, cudaMemcpyAsync(d_v, val, nnz * 4, cudaMemcpyHostToDevice, s));
+  }
+  if (cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_x, x, cols * 4, cudaMemcpyHostToDevice, s));
+  st = swb_spmv(ctx, o, rows, cols, nnz, d_rp, d_ci, d_v, d_x, d_y, s);
+  if (st != SWB_OK) return st;
+  if (rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(y, d_y, rows * 4, cudaMemcpyDeviceToHost, s));
+  SWB_CUDA(ctx, cudaStreamSynchronize(s));
+  return SWB_OK;
+}
+
+int swb_spmm_host(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz, int64_t n_rhs,
+                  const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *B, float *C) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = check_csr_sizes(ctx, "spmm", rows, cols, nnz);
+  if (st != SWB_OK) return st;
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  if (!row_ptr || (nnz > 0 && (!col_idx || !val)) || (cols > 0 && !B) || (rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  size_t need = pad256((rows + 1) * 4) + 2 * pad256(nnz * 4) + pad256(cols * n_rhs * 4) + pad256(rows * n_rhs * 4);
+  st = workspace_reserve(ctx, need);
+  if (st != SWB_OK) return st;
+  int32_t *d_rp = workspace_take<int32_t>(ctx, rows + 1);
+  int32_t *d_ci = workspace_take<int32_t>(ctx, nnz);
+  float *d_v = workspace_take<float>(ctx, nnz);
+  float *d_B = workspace_take<float>(ctx, cols * n_rhs);
+  float *d_C = workspace_take<float>(ctx, rows * n_rhs);
+  cudaStream_t s = ctx->host_stream;
+  SWB_CUDA(ctx, cudaMemcpyAsync(d_rp, row_ptr, (rows + 1) * 4, cudaMemcpyHostToDevice, s));
+  if (nnz > 0) {
+    SWB_CUDA(ctx, cudaMemcpyAsync(d_ci, col_idx, nnz * 4, cudaMemcpyHostToDevice, s));
+    SWB_CUDA(ctx, cudaMemcpyAsync(d_v, val, nnz * 4, cudaMemcpyHostToDevice, s));
+  }
+  if (cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_B, B, cols * n_rhs * 4, cudaMemcpyHostToDevice, s));
+  st = swb_spmm(ctx, o, rows, cols, nnz, n_rhs, d_rp, d_ci, d_v, d_B, d_C, s);
+  if (st != SWB_OK) return st;
+  if (rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(C, d_C, rows * n_rhs * 4, cudaMemcpyDeviceToHost, s));
+  SWB_CUDA(ctx, cudaStreamSynchronize(s));
+  return SWB_OK;
+}
+
+int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnzb,
+                           int64_t bs, int64_t n_rhs, const int32_t *brp, const int32_t *bci,
+                           const uint16_t *bv, const uint16_t *B, uint16_t *C) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = check_bsr(ctx, rows, cols, nnzb, bs, n_rhs);
+  if (st != SWB_OK) return st;
+  if (!brp || (nnzb > 0 && (!bci || !bv)) || (cols > 0 && !B) || (rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: NULL operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  const int64_t brows = rows / bs;
+  size_t need = pad256((brows + 1) * 4) + pad256(nnzb * 4) + pad256(nnzb * bs * bs * 2) +
+                pad256(cols * n_rhs * 2) + pad256(rows * n_rhs * 2);
+  st = workspace_reserve(ctx, need);
+  if (st != SWB_OK) return st;
+  int32_t *d_rp = workspace_take<int32_t>(ctx, brows + 1);
+  int32_t *d_ci = workspace_take<int32_t>(ctx, nnzb);
+  uint16_t *d_v = workspace_take<uint16_t>(ctx, nnzb * bs * bs);
+  uint16_t *d_B = workspace_take<uint16_t>(ctx, cols * n_rhs);
+  uint16_t *d_C = workspace_take<uint16_t>(ctx, rows * n_rhs);
+  cudaStream_t s = ctx->host_stream;
+  SWB_CUDA(ctx, cudaMemcpyAsync(d_rp, brp, (brows + 1) * 4, cudaMemcpyHostToDevice, s));
+  if (nnzb > 0) {
+    SWB_CUDA(ctx, cudaMemcpyAsync(d_ci, bci, nnzb * 4, cudaMemcpyHostToDevice, s));
+    SWB_CUDA(ctx, cudaMemcpyAsync(d_v, bv, nnzb * bs * bs * 2, cudaMemcpyHostToDevice, s));
+  }
+  if (cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_B, B, cols * n_rhs * 2, cudaMemcpyHostToDevice, s));
+  st = swb_bsr_spmm_bf16(ctx, o, rows, cols, nnzb, bs, n_rhs, d_rp, d_ci, d_v, d_B, d_C, s);
+  if (st != SWB_OK) return st;
+  if (rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(C, d_C, rows * n_rhs * 2, cudaMemcpyDeviceToHost, s));
+  SWB_CUDA(ctx, cudaStreamSynchronize(s));
+  return SWB_OK;
+}
+
+// ---- memref-descriptor entry points -------------------------------------------------
+
+static swb_context *process_context() {
+  static swb_context *ctx = nullptr;
+  if (!ctx) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (swb_create(&ctx, device) != SWB_OK) {
+      fprintf(stderr, "sparsewave_b200: %s\n", swb_last_error(nullptr));
+      abort();
+    }
+  }
+  return ctx;
+}
+
+static void env_options(swb_context *ctx, swb_options *o) {
+  swb_options_default(o);
+  const char *text = getenv("SPARSEWAVE_B200_OPTIONS");
+  if (text && swb_options_parse(ctx, o, text) != SWB_OK) {
+    fprintf(stderr, "sparsewave_b200: %s\n", swb_last_error(ctx));
+    abort();
+  }
+}
+
+int swb_spmv_memref(swb_context *ctx, const swb_options *o, swb_memref_1d_i32 *rp, swb_memref_1d_i32 *ci,
+                    swb_memref_1d_f32 *v, swb_memref_1d_f32 *x, swb_memref_1d_f32 *y, swb_stream stream) {
+  if (!rp || !ci || !v || !x || !y) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL memref descriptor");
+  if (rp->strides[0] != 1 || ci->strides[0] != 1 || v->strides[0] != 1 || x->strides[0] != 1 || y->strides[0] != 1)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmv: memref has an unexpected layout");
+  // SparseWaveOps.cpp:83-108
+  if (ci->sizes[0] != v->sizes[0])
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.spmv' op column indices and values must have the same size, but got %lld and %lld",
+                (long long)ci->sizes[0], (long long)v->sizes[0]);
+  if (rp->sizes[0] != y->sizes[0] + 1)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.spmv' op row offsets size must equal output size plus one, but got %lld and %lld",
+                (long long)rp->sizes[0], (long long)y->sizes[0]);
+  return swb_spmv(ctx, o, y->sizes[0], x->sizes[0], v->sizes[0], rp->data + rp->offset, ci->data + ci->offset,
+                  v->data + v->offset, x->data + x->offset, y->data + y->offset, stream);
+}
+
+static bool identity2d(const swb_memref_2d_f32 *m) { return m->strides[1] == 1 && m->strides[0] == m->sizes[1]; }
+
+int swb_spmm_memref(swb_context *ctx, const swb_options *o, swb_memref_1d_i32 *rp, swb_memref_1d_i32 *ci,
+                    swb_memref_1d_f32 *v, swb_memref_2d_f32 *rhs, swb_memref_2d_f32 *out, swb_stream stream) {
+  if (!rp || !ci || !v || !rhs || !out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL memref descriptor");
+  if (rp->strides[0] != 1 || ci->strides[0] != 1 || v->strides[0] != 1)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: memref has an unexpected layout");
+  if (!identity2d(rhs)) return fail(ctx, SWB_ERR_INVALID_SHAPE, "RHS memref has an unexpected layout");
+  if (!identity2d(out)) return fail(ctx, SWB_ERR_INVALID_SHAPE, "output memref has an unexpected layout");
+  if (ci->sizes[0] != v->sizes[0])
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.spmm' op column indices and values must have the same size, but got %lld and %lld",
+                (long long)ci->sizes[0], (long long)v->sizes[0]);
+  if (rp->sizes[0] != out->sizes[0] + 1)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.spmm' op row offsets size must equal output rows plus one, but got %lld and %lld",
+                (long long)rp->sizes[0], (long long)out->sizes[0]);
+  if (rhs->sizes[1] != out->sizes[1])
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.spmm' op right-hand side and output must have the same number of columns");
+  return swb_spmm(ctx, o, out->sizes[0], rhs->sizes[0], v->sizes[0], out->sizes[1], rp->data + rp->offset,
+                  ci->data + ci->offset, v->data + v->offset, rhs->data + rhs->offset, out->data + out->offset,
+                  stream);
+}
+
+int swb_bsr_spmm_memref(swb_context *ctx, const swb_options *o, swb_memref_1d_i32 *brp, swb_memref_1d_i32 *bci,
+                        swb_memref_1d_f32 *bv, swb_memref_2d_f32 *rhs, swb_memref_2d_f32 *out, int64_t bs,
+                        swb_stream stream) {
+  if (!brp || !bci || !bv || !rhs || !out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: NULL memref descriptor");
+  if (brp->strides[0] != 1 || bci->strides[0] != 1 || bv->strides[0] != 1)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "bsr_spmm: memref has an unexpected layout");
+  if (!identity2d(rhs)) return fail(ctx, SWB_ERR_INVALID_SHAPE, "RHS memref has an unexpected layout");
+  if (!identity2d(out)) return fail(ctx, SWB_ERR_INVALID_SHAPE, "output memref has an unexpected layout");
+  // verifyBSRStorage (SparseWaveOps.cpp:144-207)
+  if (bs <= 0) return fail(ctx, SWB_ERR_INVALID_SHAPE, "'sparsewave.bsr_spmm' op block size must be positive, but got %lld", (long long)bs);
+  if (out->sizes[0] % bs != 0)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.bsr_spmm' op output rows must be divisible by block size, but got %lld and %lld",
+                (long long)out->sizes[0], (long long)bs);
+  if (brp->sizes[0] != out->sizes[0] / bs + 1)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.bsr_spmm' op block-row offsets size must equal the number of block rows plus one, but got %lld and %lld",
+                (long long)brp->sizes[0], (long long)(out->sizes[0] / bs));
+  if (bv->sizes[0] != bci->sizes[0] * bs * bs)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.bsr_spmm' op block values size must equal the number of blocks times block_size squared, but got %lld and %lld blocks",
+                (long long)bv->sizes[0], (long long)bci->sizes[0]);
+  if (rhs->sizes[1] != out->sizes[1])
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.bsr_spmm' op right-hand side and output must have the same number of columns");
+  if (rhs->sizes[0] % bs != 0)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE,
+                "'sparsewave.bsr_spmm' op right-hand-side rows must be divisible by block size, but got %lld and %lld",
+                (long long)rhs->sizes[0], (long long)bs);
+  return swb_bsr_spmm_f32(ctx, o, out->sizes[0], rhs->sizes[0], bci->sizes[0], bs, out->sizes[1],
+                          brp->data + brp->offset, bci->data + bci->offset, bv->data + bv->offset,
+                          rhs->data + rhs->offset, out->data + out->offset, stream);
+}
+
+static void finish_ciface(swb_context *ctx, int st) {
+  if (st == SWB_OK) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) return;
+    fprintf(stderr, "sparsewave_b200: CUDA error: %s\n", cudaGetErrorString(e));
+    abort();
+  }
+  fprintf(stderr, "sparsewave_b200: %s\n", swb_last_error(ctx));
+  abort();
+}
+
+void _mlir_ciface_sparsewave_spmv(swb_memref_1d_i32 *rp, swb_memref_1d_i32 *ci, swb_memref_1d_f32 *v,
+                                  swb_memref_1d_f32 *x, swb_memref_1d_f32 *y) {
+  swb_context *ctx = process_context();
+  swb_options o;
+  env_options(ctx, &o);
+  finish_ciface(ctx, swb_spmv_memref(ctx, &o, rp, ci, v, x, y, nullptr));
+}
+
+void _mlir_ciface_sparsewave_spmm(swb_memref_1d_i32 *rp, swb_memref_1d_i32 *ci, swb_memref_1d_f32 *v,
+                                  swb_memref_2d_f32 *rhs, swb_memref_2d_f32 *out) {
+  swb_context *ctx = process_context();
+  swb_options o;
+  env_options(ctx, &o);
+  finish_ciface(ctx, swb_spmm_memref(ctx, &o, rp, ci, v, rhs, out, nullptr));
+}
+
+void _mlir_ciface_sparsewave_bsr_spmm(swb_memref_1d_i32 *brp, swb_memref_1d_i32 *bci, swb_memref_1d_f32 *bv,
+                                      swb_memref_2d_f32 *rhs, swb_memref_2d_f32 *out, int64_t bs) {
+  swb_context *ctx = process_context();
+  swb_options o;
+  env_options(ctx, &o);
+  finish_ciface(ctx, swb_bsr_spmm_memref(ctx, &o, brp, bci, bv, rhs, out, bs, nullptr));
+}
+
+// ---- bundle-style launch ----------------------------------------------------------------
+
+int swb_bundle_launch(swb_context *ctx, const char *operation, int64_t n, void *const args[5], swb_stream stream) {
+  if (!ctx) return fail(nullptr, SWB_ERR_INVALID_ARGUMENT, "context is NULL");
+  if (!operation || strcmp(operation, "spmm") != 0)
+    return fail(ctx, SWB_ERR_UNSUPPORTED, "input application is %s, but the bundle supports spmm", operation ? operation : "(null)");
+  if (!args) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bundle launch: args is NULL");
+  if (n < 0) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bundle launch: n must be non-negative");
+  // Launch contract of the fixed-shape bundle: wave-per-row-tile, block 64,
+  // tile 4, N == 4 (tools/sparsewave-bundle/sparsewave_bundle_ir.py:4-9).
+  // The bundle kernel takes bare pointers, so the reduction extent (rows of
+  // rhs) and NNZ are not part of the contract; they only matter for argument
+  // checks here and are passed as upper bounds.
+  swb_options o;
+  swb_options_default(&o);
+  o.spmm_mapping = SWB_WAVE_PER_ROW_TILE;
+  o.spmm_block_size = 64;
+  o.spmm_tile_size = 4;
+  return swb_spmm(ctx, &o, n, kI32Max, kI32Max, 4, static_cast<const int32_t *>(args[0]),
+                  static_cast<const int32_t *>(args[1]), static_cast<const float *>(args[2]),
+                  static_cast<const float *>(args[3]), static_cast<float *>(args[4]), stream);
+}
+
+// ---- sharding -------------------------------------------------------------------------------
+
+int swb_shard_rows_by_nnz(swb_context *ctx, const int32_t *row_ptr, int64_t rows, int64_t n_shards,
+                          int64_t *boundaries) {
+  if (!row_ptr || !boundaries) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "shard: NULL pointer");
+  if (rows < 0 || n_shards < 1) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "shard: rows must be non-negative and n_shards positive");
+  const int64_t nnz = row_ptr[rows];
+  boundaries[0] = 0;
+  for (int64_t k = 1; k < n_shards; ++k) {
+    // floor(k * nnz / n_shards) without overflow: nnz < 2^31, k <= n_shards.
+    const int64_t target = (int64_t)(((__int128)k * nnz) / n_shards);
+    // first row r with row_ptr[r] >= target
+    int64_t lo = 0, hi = rows;
+    while (lo < hi) {
+      int64_t mid = lo + (hi - lo) / 2;
+      if (row_ptr[mid] < target) lo = mid + 1; else hi = mid;
+    }
+    boundaries[k] = lo < boundaries[k - 1] ? boundaries[k - 1] : lo;
+  }
+  boundaries[n_shards] = rows;
+  return SWB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,101 @@
+// Internal launch interface between the C-ABI dispatcher (swb_api.cu) and the
+// kernel translation units.  All pointers are device pointers; every launcher
+// enqueues on `stream`, adds the number of kernels it launched to *launches
+// and returns the CUDA status of the launch.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace swb {
+
+struct CsrSpmvArgs {
+  int64_t rows, cols, nnz;
+  const int32_t *row_ptr;
+  const int32_t *col_idx;
+  const float *val;
+  const float *x;
+  float *y;
+};
+
+struct CsrSpmmArgs {
+  int64_t rows, cols, nnz, n_rhs;
+  const int32_t *row_ptr;
+  const int32_t *col_idx;
+  const float *val;
+  const float *B;
+  float *C;
+};
+
+struct BsrSpmmArgs {
+  int64_t rows, cols, nnzb, block_size, n_rhs;
+  const int32_t *block_row_ptr;
+  const int32_t *block_col_idx;
+  const void *block_values;  // f32 or bf16
+  const void *B;
+  void *C;
+};
+
+// Optional per-position trace of a position-mapped SpMV (all nnz entries).
+struct PositionTrace {
+  int32_t *row_of_position = nullptr;
+  int32_t *worker_of_position = nullptr;
+  int32_t *segment_end = nullptr;
+  bool enabled() const { return row_of_position != nullptr; }
+};
+
+struct DeviceInfo {
+  int sm_count = 148;
+  int max_smem_optin = 0;
+};
+
+// y[i] = 0 (the separate initialisation launch of the position schedules).
+cudaError_t launch_fill_zero(float *y, int64_t n, int block, cudaStream_t s,
+                             int64_t *launches);
+
+// --- SpMV row mappings
+cudaError_t launch_spmv_thread_per_row(const CsrSpmvArgs &a, int block,
+                                       cudaStream_t s, int64_t *launches);
+cudaError_t launch_spmv_wave_per_row(const CsrSpmvArgs &a, int block,
+                                     cudaStream_t s, int64_t *launches);
+cudaError_t launch_spmv_block_per_row(const CsrSpmvArgs &a, int block,
+                                      cudaStream_t s, int64_t *launches);
+
+// --- SpMV position mappings (each also launches the zero fill)
+cudaError_t launch_spmv_thread_per_position(const CsrSpmvArgs &a, int block,
+                                            int64_t chunk, bool segmented,
+                                            const PositionTrace &trace,
+                                            cudaStream_t s, int64_t *launches);
+// `batch`: consecutive reference wave partitions walked by one warp (>= 1).
+cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block,
+                                          int64_t batch,
+                                          const PositionTrace &trace,
+                                          cudaStream_t s, int64_t *launches,
+                                          int64_t *physical_grid);
+int64_t wave_per_position_auto_batch(int64_t nnz, int block,
+                                     const DeviceInfo &dev);
+int64_t wave_per_position_physical_grid(int64_t nnz, int block, int64_t batch);
+
+// --- SpMM
+cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block,
+                                          cudaStream_t s, int64_t *launches);
+cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block,
+                                          int tile, cudaStream_t s,
+                                          int64_t *launches);
+cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block,
+                                            int64_t chunk, cudaStream_t s,
+                                            int64_t *launches);
+
+// --- BSR SpMM
+cudaError_t launch_bsr_spmm_thread_per_output_f32(const BsrSpmmArgs &a,
+                                                  int block, cudaStream_t s,
+                                                  int64_t *launches);
+cudaError_t launch_bsr_spmm_thread_per_output_bf16(const BsrSpmmArgs &a,
+                                                   int block, cudaStream_t s,
+                                                   int64_t *launches);
+// 16x16 bf16 blocks on the tcgen05 tensor cores.  `status_flag` is a device
+// int the kernel sets non-zero when one of its bounded waits gives up.
+cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag,
+                                      const DeviceInfo &dev, cudaStream_t s,
+                                      int64_t *launches);
+
+}  // namespace swb

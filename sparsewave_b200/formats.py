@@ -1,0 +1,198 @@
+"""On-disk matrix formats of the SparseWave benchmark tooling.
+
+Binary layouts (little endian), as written by benchmark/benchmark_utils.py and
+read by benchmark/SparseBenchmarkUtils.cpp in the SparseWave tree:
+
+* ``SWCSR001``: magic, ``<QQQ`` rows/columns/nnz, ``i32[rows+1]`` row offsets,
+  ``i32[nnz]`` column indices, ``f32[nnz]`` values
+  (benchmark_utils.py:180-211, SparseBenchmarkUtils.cpp:83-124).
+* ``SWCOO001``: magic, ``<QQQ``, ``i32[nnz]`` rows, ``i32[nnz]`` columns,
+  ``f32[nnz]`` values (benchmark_utils.py:214-237).
+* ``SWBSR001``: magic, ``<QQQQQQQ`` padded rows/columns, nnzb, block size,
+  original rows/columns/nnz, ``i32[rows/bs+1]`` block-row offsets,
+  ``i32[nnzb]`` block columns, ``f32[nnzb*bs*bs]`` block values, then the
+  original COO entries ``i32[nnz]``, ``i32[nnz]``, ``f32[nnz]``
+  (benchmark_utils.py:315-379, SparseBenchmarkUtils.cpp:142-185).
+"""
+from __future__ import annotations
+
+import struct
+from pathlib import Path
+
+import numpy as np
+
+CSR_MAGIC = b"SWCSR001"
+COO_MAGIC = b"SWCOO001"
+BSR_MAGIC = b"SWBSR001"
+_I32_MAX = (1 << 31) - 1
+
+
+def write_csr_binary(path, rows: int, cols: int, row_ptr, col_idx, values) -> None:
+    row_ptr = np.ascontiguousarray(row_ptr, dtype="<i4")
+    col_idx = np.ascontiguousarray(col_idx, dtype="<i4")
+    values = np.ascontiguousarray(values, dtype="<f4")
+    nnz = len(values)
+    if rows > _I32_MAX or nnz > _I32_MAX:
+        raise ValueError("matrix rows and NNZ must fit in the i32 CSR type")
+    if len(row_ptr) != rows + 1 or len(col_idx) != nnz:
+        raise ValueError("CSR arrays have inconsistent sizes")
+    with Path(path).open("wb") as f:
+        f.write(CSR_MAGIC)
+        f.write(struct.pack("<QQQ", rows, cols, nnz))
+        f.write(row_ptr.tobytes())
+        f.write(col_idx.tobytes())
+        f.write(values.tobytes())
+
+
+def read_csr_binary(path):
+    """Returns (rows, cols, row_ptr, col_idx, values)."""
+    data = Path(path).read_bytes()
+    if data[:8] != CSR_MAGIC:
+        raise ValueError("invalid CSR binary header")
+    rows, cols, nnz = struct.unpack_from("<QQQ", data, 8)
+    off = 32
+    need = off + 4 * (rows + 1) + 8 * nnz
+    if len(data) < need:
+        raise ValueError("could not read CSR arrays: file is truncated")
+    row_ptr = np.frombuffer(data, "<i4", rows + 1, off); off += 4 * (rows + 1)
+    col_idx = np.frombuffer(data, "<i4", nnz, off); off += 4 * nnz
+    values = np.frombuffer(data, "<f4", nnz, off)
+    return rows, cols, row_ptr.copy(), col_idx.copy(), values.copy()
+
+
+def write_coo_binary(path, rows: int, cols: int, row_idx, col_idx, values) -> None:
+    row_idx = np.ascontiguousarray(row_idx, dtype="<i4")
+    col_idx = np.ascontiguousarray(col_idx, dtype="<i4")
+    values = np.ascontiguousarray(values, dtype="<f4")
+    if rows > _I32_MAX or cols > _I32_MAX or len(values) > _I32_MAX:
+        raise ValueError("matrix dimensions and NNZ must fit in the i32 COO type")
+    with Path(path).open("wb") as f:
+        f.write(COO_MAGIC)
+        f.write(struct.pack("<QQQ", rows, cols, len(values)))
+        f.write(row_idx.tobytes())
+        f.write(col_idx.tobytes())
+        f.write(values.tobytes())
+
+
+def convert_to_bsr(rows: int, cols: int, row_idx, col_idx, values, block_size: int) -> dict:
+    """COO entries -> padded BSR; duplicate coordinates are summed into their
+    slot, blocks are ordered by (block row, block column)
+    (convert_to_bsr, benchmark_utils.py:240-312)."""
+    if block_size <= 0:
+        raise ValueError("BSR block size must be positive")
+    bs = block_size
+    row_idx = np.asarray(row_idx, dtype=np.int64)
+    col_idx = np.asarray(col_idx, dtype=np.int64)
+    values = np.asarray(values, dtype=np.float64)
+    padded_rows = -(-rows // bs) * bs
+    padded_cols = -(-cols // bs) * bs
+    brows, bcols = padded_rows // bs, padded_cols // bs
+    bkey = (row_idx // bs) * max(bcols, 1) + (col_idx // bs)
+    uniq, inverse = np.unique(bkey, return_inverse=True)
+    nnzb = len(uniq)
+    block_values = np.zeros((nnzb, bs, bs), dtype=np.float64)
+    np.add.at(block_values, (inverse, row_idx % bs, col_idx % bs), values)
+    block_rows = uniq // max(bcols, 1)
+    block_cols = uniq % max(bcols, 1)
+    brp = np.zeros(brows + 1, dtype=np.int64)
+    np.add.at(brp, block_rows + 1, 1)
+    brp = np.cumsum(brp)
+    occupied = len(np.unique(row_idx * max(padded_cols, 1) + col_idx))
+    slots = nnzb * bs * bs
+    return {
+        "rows": padded_rows, "columns": padded_cols, "original_rows": rows, "original_columns": cols,
+        "nnz": len(values), "block_size": bs, "nnzb": nnzb,
+        "block_row_offsets": brp.astype(np.int32), "block_column_indices": block_cols.astype(np.int32),
+        "block_values": block_values.reshape(-1).astype(np.float32),
+        "input_row_indices": row_idx.astype(np.int32), "input_column_indices": col_idx.astype(np.int32),
+        "input_values": values.astype(np.float32),
+        "block_density": nnzb / (brows * bcols) if brows and bcols else 0.0,
+        "internal_zero_fraction": 1.0 - occupied / slots if slots else 0.0,
+        "storage_overhead": slots / occupied if occupied else 0.0,
+    }
+
+
+def write_bsr_binary(path, m: dict) -> None:
+    for k in ("rows", "columns", "nnzb", "original_rows", "original_columns", "nnz"):
+        if m[k] > _I32_MAX:
+            raise ValueError("BSR dimensions and NNZ blocks must fit in i32")
+    with Path(path).open("wb") as f:
+        f.write(BSR_MAGIC)
+        f.write(struct.pack("<QQQQQQQ", m["rows"], m["columns"], m["nnzb"], m["block_size"],
+                            m["original_rows"], m["original_columns"], m["nnz"]))
+        f.write(np.ascontiguousarray(m["block_row_offsets"], "<i4").tobytes())
+        f.write(np.ascontiguousarray(m["block_column_indices"], "<i4").tobytes())
+        f.write(np.ascontiguousarray(m["block_values"], "<f4").tobytes())
+        f.write(np.ascontiguousarray(m["input_row_indices"], "<i4").tobytes())
+        f.write(np.ascontiguousarray(m["input_column_indices"], "<i4").tobytes())
+        f.write(np.ascontiguousarray(m["input_values"], "<f4").tobytes())
+
+
+def read_bsr_binary(path) -> dict:
+    data = Path(path).read_bytes()
+    if data[:8] != BSR_MAGIC:
+        raise ValueError("invalid BSR binary header")
+    rows, cols, nnzb, bs, orows, ocols, nnz = struct.unpack_from("<QQQQQQQ", data, 8)
+    if bs == 0 or rows % bs or cols % bs:
+        raise ValueError("BSR dimensions must be divisible by a positive block size")
+    if orows > rows or ocols > cols:
+        raise ValueError("original BSR dimensions exceed the padded dimensions")
+    off = 8 + 7 * 8
+
+    def take(dtype, count):
+        nonlocal off
+        a = np.frombuffer(data, dtype, count, off).copy()
+        off += a.nbytes
+        return a
+
+    return {
+        "rows": rows, "columns": cols, "nnzb": nnzb, "block_size": bs, "original_rows": orows,
+        "original_columns": ocols, "nnz": nnz,
+        "block_row_offsets": take("<i4", rows // bs + 1), "block_column_indices": take("<i4", nnzb),
+        "block_values": take("<f4", nnzb * bs * bs), "input_row_indices": take("<i4", nnz),
+        "input_column_indices": take("<i4", nnz), "input_values": take("<f4", nnz),
+    }
+
+
+def read_matrix_market(path) -> dict:
+    """Coordinate Matrix Market file -> COO with 0-based indices; `symmetric`
+    and `skew-symmetric` files are expanded, `pattern` entries get value 1
+    (benchmark_utils.py:56-177)."""
+    with Path(path).open("r", encoding="utf-8") as f:
+        header = f.readline().strip().split()
+        if len(header) != 5 or header[0] != "%%MatrixMarket" or header[1] != "matrix":
+            raise ValueError("expected a Matrix Market matrix header")
+        layout, field, symmetry = header[2].lower(), header[3].lower(), header[4].lower()
+        if layout != "coordinate":
+            raise ValueError("only coordinate Matrix Market files are supported")
+        if field not in ("real", "integer", "pattern"):
+            raise ValueError(f"unsupported Matrix Market field: {field}")
+        if symmetry not in ("general", "symmetric", "skew-symmetric"):
+            raise ValueError(f"unsupported Matrix Market symmetry: {symmetry}")
+        line = f.readline()
+        while line.startswith("%") or not line.strip():
+            line = f.readline()
+        rows, cols, entries = (int(t) for t in line.split())
+        ri, ci, va = [], [], []
+        for _ in range(entries):
+            parts = f.readline().split()
+            r, c = int(parts[0]) - 1, int(parts[1]) - 1
+            v = 1.0 if field == "pattern" else float(parts[2])
+            if not (0 <= r < rows and 0 <= c < cols):
+                raise ValueError("Matrix Market coordinate is out of bounds")
+            ri.append(r); ci.append(c); va.append(v)
+            if symmetry != "general" and r != c:
+                ri.append(c); ci.append(r); va.append(-v if symmetry == "skew-symmetric" else v)
+    return {"rows": rows, "columns": cols, "row_indices": np.array(ri, np.int32),
+            "column_indices": np.array(ci, np.int32), "values": np.array(va, np.float32)}
+
+
+def coo_to_csr(rows: int, row_idx, col_idx, values):
+    """Stable sort by (row, column); duplicates are kept as separate entries."""
+    row_idx = np.asarray(row_idx, np.int64)
+    col_idx = np.asarray(col_idx, np.int64)
+    order = np.lexsort((col_idx, row_idx))
+    rp = np.zeros(rows + 1, np.int64)
+    np.add.at(rp, row_idx + 1, 1)
+    return (np.cumsum(rp).astype(np.int32), col_idx[order].astype(np.int32),
+            np.asarray(values, np.float32)[order])
