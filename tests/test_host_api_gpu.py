@@ -1,0 +1,113 @@
+"""Host-buffer entry points, memref-descriptor entry points and argument errors on the GPU."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from sparsewave_b200 import SparseWaveError, _lib, make_options
+from tests.helpers import BSR_GOLDEN, SPMM_GOLDEN, SPMV_GOLDEN, assert_within_bound, dev, random_csr
+
+pytestmark = pytest.mark.gpu
+
+
+def test_spmv_host_buffers(ctx):
+    rp, ci, v = random_csr(2000, 1500, 11, seed=9)
+    x = np.random.default_rng(9).uniform(-1, 1, 1500).astype(np.float32)
+    for opts in ("mapping=wave-per-row block-size=128", "mapping=wave-per-position", "mapping=thread-per-row"):
+        y = np.full(2000, np.nan, np.float32)
+        ctx.spmv_host(opts, rp, ci, v, x, y)
+        assert_within_bound(y, oracle.csr_spmv(rp, ci, v, x), oracle.csr_abs_bound(rp, ci, v, x))
+    # pinned torch tensors work the same way; a second, larger call regrows the workspace
+    rp2, ci2, v2 = random_csr(9000, 1500, 14, seed=10)
+    t = [torch.from_numpy(a).pin_memory() for a in (rp2, ci2, v2, x)]
+    y = torch.empty(9000, dtype=torch.float32).pin_memory()
+    ctx.spmv_host("mapping=wave-per-row", *t, y)
+    assert_within_bound(y.numpy(), oracle.csr_spmv(rp2, ci2, v2, x), oracle.csr_abs_bound(rp2, ci2, v2, x))
+
+
+def test_spmm_and_bsr_host_buffers(ctx):
+    rp, ci, v = random_csr(1200, 800, 10, seed=12)
+    B = np.random.default_rng(12).uniform(-1, 1, (800, 8)).astype(np.float32)
+    Cout = np.empty((1200, 8), np.float32)
+    ctx.spmm_host("spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=64", rp, ci, v, B, Cout)
+    assert_within_bound(Cout, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+    g = BSR_GOLDEN
+    bv = torch.tensor(g["bv"], dtype=torch.bfloat16)
+    Bb = torch.tensor(g["B"], dtype=torch.bfloat16)
+    out = torch.empty((4, 2), dtype=torch.bfloat16)
+    ctx.bsr_spmm_bf16_host("", torch.tensor(g["brp"], dtype=torch.int32), torch.tensor(g["bci"], dtype=torch.int32),
+                           bv, Bb, g["bs"], out)
+    assert out.float().tolist() == [[17, 170], [45, 450], [7, 70], [16, 160]]
+
+
+def _m1(t):
+    return _lib.Memref1D(t.data_ptr(), t.data_ptr(), 0, (C.c_int64 * 1)(t.numel()), (C.c_int64 * 1)(1))
+
+
+def _m2(t):
+    return _lib.Memref2D(t.data_ptr(), t.data_ptr(), 0, (C.c_int64 * 2)(*t.shape), (C.c_int64 * 2)(t.shape[1], 1))
+
+
+def test_memref_entry_points(ctx):
+    lib = _lib.load()
+    g = SPMV_GOLDEN
+    t = [dev(g["row_ptr"], torch.int32), dev(g["col"], torch.int32), dev(g["val"], torch.float32),
+         dev(g["x"], torch.float32), torch.zeros(5, device="cuda")]
+    d = [_m1(a) for a in t]
+    o = make_options("mapping=wave-per-row block-size=128")
+    st = lib.swb_spmv_memref(ctx._ctx, C.byref(o), *[C.byref(m) for m in d], None)
+    torch.cuda.synchronize()
+    assert st == 0 and t[4].cpu().tolist() == g["y"]
+    # the emit_c_interface symbol itself (process-wide context, options from the environment)
+    t[4].zero_()
+    lib._mlir_ciface_sparsewave_spmv(*[C.byref(m) for m in d])
+    assert t[4].cpu().tolist() == g["y"]
+    # verifier diagnostics (SparseWaveOps.cpp:83-108)
+    bad = _m1(torch.zeros(4, device="cuda"))
+    st = lib.swb_spmv_memref(ctx._ctx, C.byref(o), C.byref(d[0]), C.byref(d[1]), C.byref(d[2]), C.byref(d[3]),
+                             C.byref(bad), None)
+    assert st == _lib.SWB_ERR_INVALID_SHAPE
+    assert b"row offsets size must equal output size plus one, but got 6 and 4" in lib.swb_last_error(ctx._ctx)
+    short = _m1(torch.zeros(5, device="cuda"))
+    st = lib.swb_spmv_memref(ctx._ctx, C.byref(o), C.byref(d[0]), C.byref(d[1]), C.byref(short), C.byref(d[3]),
+                             C.byref(d[4]), None)
+    assert b"column indices and values must have the same size, but got 6 and 5" in lib.swb_last_error(ctx._ctx)
+
+    g = SPMM_GOLDEN
+    t = [dev(g["row_ptr"], torch.int32), dev(g["col"], torch.int32), dev(g["val"], torch.float32),
+         dev(g["B"], torch.float32), torch.zeros((2, 2), device="cuda")]
+    st = lib.swb_spmm_memref(ctx._ctx, C.byref(make_options("spmm-mapping=wave-per-row-tile spmm-block-size=64")),
+                             C.byref(_m1(t[0])), C.byref(_m1(t[1])), C.byref(_m1(t[2])), C.byref(_m2(t[3])),
+                             C.byref(_m2(t[4])), None)
+    torch.cuda.synchronize()
+    assert st == 0 and t[4].cpu().tolist() == g["C"]
+
+    g = BSR_GOLDEN
+    t = [dev(g["brp"], torch.int32), dev(g["bci"], torch.int32), dev(g["bv"], torch.float32),
+         dev(g["B"], torch.float32), torch.zeros((4, 2), device="cuda")]
+    args = [C.byref(_m1(t[0])), C.byref(_m1(t[1])), C.byref(_m1(t[2])), C.byref(_m2(t[3])), C.byref(_m2(t[4]))]
+    st = lib.swb_bsr_spmm_memref(ctx._ctx, C.byref(make_options("spmm-block-size=64")), *args, 2, None)
+    torch.cuda.synchronize()
+    assert st == 0 and t[4].cpu().tolist() == g["C"]
+    st = lib.swb_bsr_spmm_memref(ctx._ctx, C.byref(make_options("")), *args, 3, None)
+    assert st == _lib.SWB_ERR_INVALID_SHAPE
+    assert b"output rows must be divisible by block size, but got 4 and 3" in lib.swb_last_error(ctx._ctx)
+
+
+def test_argument_errors(ctx):
+    g = SPMV_GOLDEN
+    t = [dev(g["row_ptr"], torch.int32), dev(g["col"], torch.int32), dev(g["val"], torch.float32),
+         dev(g["x"], torch.float32)]
+    with pytest.raises(SparseWaveError, match="wave-per-row requires the SpMV block size to be a multiple of 32"):
+        ctx.spmv("mapping=wave-per-row block-size=48", *t)
+    with pytest.raises(SparseWaveError, match="block size must be positive"):
+        ctx.bsr_spmm("", t[0], t[1], torch.zeros(0, device="cuda"), torch.zeros((4, 2), device="cuda"), 0)
+    with pytest.raises(SparseWaveError, match="bundle supports spmm"):
+        ctx.bundle_launch("spmv", 5, t + [t[3]])
+    with pytest.raises(TypeError):
+        ctx.spmv("", t[0].cpu(), t[1], t[2], t[3])
+    before = ctx.kernel_launches
+    ctx.spmv("mapping=wave-per-position", *t)
+    assert ctx.kernel_launches == before + 2  # zero fill + compute

@@ -1,0 +1,149 @@
+"""CSR SpMM and BSR SpMM parity on the GPU, through the C ABI, against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from sparsewave_b200 import workloads as W
+from tests.helpers import (BSR_GOLDEN, SPMM_GOLDEN, SPMM_GOLDEN_TORCH, assert_within_bound, dev, random_csr)
+
+pytestmark = pytest.mark.gpu
+
+# spmm-sparse-tensor-runtime.mlir:2-29 runs these four pipelines (tile 4 > N = 2 exercises the tail path)
+SPMM_GOLDEN_OPTIONS = [
+    "spmm-mapping=thread-per-output spmm-block-size=64",
+    "spmm-mapping=wave-per-row-tile spmm-block-size=64 spmm-tile-size=2",
+    "spmm-mapping=wave-per-row-tile spmm-block-size=64 spmm-tile-size=4",
+    "spmm-mapping=thread-per-position spmm-block-size=64 spmm-position-chunk-size=4",
+]
+
+
+def run(ctx, opts, rp, ci, v, B):
+    C = ctx.spmm(opts, dev(rp, torch.int32), dev(ci, torch.int32), dev(v, torch.float32), dev(B, torch.float32))
+    torch.cuda.synchronize()
+    return C.cpu().numpy()
+
+
+@pytest.mark.parametrize("opts", SPMM_GOLDEN_OPTIONS)
+@pytest.mark.parametrize("g", [SPMM_GOLDEN, SPMM_GOLDEN_TORCH])
+def test_runtime_goldens(ctx, opts, g):
+    C = run(ctx, opts, g["row_ptr"], g["col"], g["val"], np.array(g["B"], np.float32))
+    assert C.tolist() == g["C"]
+
+
+@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5, 8, 12, 16, 31, 32])
+@pytest.mark.parametrize("n", [1, 4, 7, 32, 64, 70])
+def test_wave_per_row_tile_all_tiles(ctx, tile, n):
+    rp, ci, v = random_csr(701, 433, 20, seed=tile * 100 + n, empty_fraction=0.15)
+    B = np.random.default_rng(4).uniform(-1, 1, (433, n)).astype(np.float32)
+    C = run(ctx, f"spmm-mapping=wave-per-row-tile spmm-tile-size={tile} spmm-block-size=64", rp, ci, v, B)
+    assert_within_bound(C, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+
+
+@pytest.mark.parametrize("block", [32, 64, 256, 1024])
+def test_thread_per_output_is_bit_exact(ctx, block):
+    rp, ci, v = random_csr(997, 600, 12, seed=block)
+    B = np.random.default_rng(5).uniform(-1, 1, (600, 5)).astype(np.float32)
+    C = run(ctx, f"spmm-mapping=thread-per-output spmm-block-size={block}", rp, ci, v, B)
+    assert np.array_equal(C, oracle.csr_spmm(rp, ci, v, B))
+
+
+@pytest.mark.parametrize("chunk", [1, 3, 4, 64])
+def test_thread_per_position(ctx, chunk):
+    rp, ci, v = random_csr(400, 300, 8, seed=chunk, empty_fraction=0.3)
+    B = np.random.default_rng(6).uniform(-1, 1, (300, 6)).astype(np.float32)
+    C = run(ctx, f"spmm-mapping=thread-per-position spmm-position-chunk-size={chunk} spmm-block-size=128", rp, ci, v, B)
+    assert_within_bound(C, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+
+
+def test_degenerate_shapes(ctx):
+    for opts in SPMM_GOLDEN_OPTIONS:
+        C = run(ctx, opts, np.zeros(5, np.int32), np.zeros(0, np.int32), np.zeros(0, np.float32),
+                np.ones((3, 2), np.float32))
+        assert C.tolist() == [[0, 0]] * 4
+        C = run(ctx, opts, np.zeros(1, np.int32), np.zeros(0, np.int32), np.zeros(0, np.float32),
+                np.ones((3, 2), np.float32))
+        assert C.shape == (0, 2)
+
+
+def test_config_c2_bundle_shape(ctx):
+    """65536 x 65536, 32 nnz per row, N = 4, wave-per-row-tile tile 4 block 64."""
+    a, B = W.config_c2(device="cuda")
+    C = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=4 spmm-block-size=64", a.row_ptr, a.col_idx,
+                 a.values, B)
+    rp, ci, v = a.numpy()
+    Bh = B.cpu().numpy()
+    assert_within_bound(C.cpu().numpy(), oracle.csr_spmm(rp, ci, v, Bh, parallel=True),
+                        oracle.csr_abs_bound(rp, ci, v, Bh))
+    # the lrrt-style launch (five bare pointers, n = output rows) gives the same result
+    C2 = torch.empty_like(C)
+    ctx.bundle_launch("spmm", a.rows, [a.row_ptr, a.col_idx, a.values, B, C2])
+    assert torch.equal(C, C2)
+
+
+@pytest.mark.parametrize("tile", [4, 8, 16])
+def test_config_c4_shape_reduced(ctx, tile):
+    """Banded-plus-random structure, N = 64, at 1/64 of the full row count."""
+    a, B = W.config_c4(device="cuda", rows=32768)
+    C = ctx.spmm(f"spmm-mapping=wave-per-row-tile spmm-tile-size={tile} spmm-block-size=256", a.row_ptr, a.col_idx,
+                 a.values, B)
+    rp, ci, v = a.numpy()
+    Bh = B.cpu().numpy()
+    assert_within_bound(C.cpu().numpy(), oracle.csr_spmm(rp, ci, v, Bh, parallel=True),
+                        oracle.csr_abs_bound(rp, ci, v, Bh))
+
+
+def test_bsr_runtime_golden(ctx):
+    g = BSR_GOLDEN
+    C = ctx.bsr_spmm("spmm-block-size=64", dev(g["brp"], torch.int32), dev(g["bci"], torch.int32),
+                     dev(g["bv"], torch.float32), dev(g["B"], torch.float32), g["bs"])
+    assert C.cpu().tolist() == g["C"]
+    Cb = ctx.bsr_spmm("spmm-block-size=64", dev(g["brp"], torch.int32), dev(g["bci"], torch.int32),
+                      dev(g["bv"], torch.float32).bfloat16(), dev(g["B"], torch.float32).bfloat16(), g["bs"])
+    assert Cb.float().cpu().tolist() == [[17, 170], [45, 450], [7, 70], [16, 160]]
+
+
+@pytest.mark.parametrize("bs", [2, 4, 8])
+def test_bsr_f32_is_bit_exact(ctx, bs):
+    a = W.random_bsr(40, 30, bs, 0.2, seed=bs, dtype=torch.float32)
+    B = W.dense_uniform((30 * bs, 9), seed=bs)
+    C = ctx.bsr_spmm("", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(), B.cuda(), bs)
+    expected = oracle.bsr_spmm_f32(a.block_row_ptr.numpy(), a.block_col_idx.numpy(), a.block_values.numpy(),
+                                   B.numpy(), bs)
+    assert np.array_equal(C.cpu().numpy(), expected)
+
+
+def _bsr_bf16_case(ctx, grid_rows, grid_cols, bs, n, density, seed):
+    a = W.random_bsr(grid_rows, grid_cols, bs, density, seed=seed)
+    B = W.dense_normal((grid_cols * bs, n), seed=seed)
+    C = ctx.bsr_spmm("", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(), B.cuda(), bs)
+    torch.cuda.synchronize()
+    bits, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.numpy(), a.block_col_idx.numpy(),
+                                     a.block_values.view(torch.uint16).numpy(), B.view(torch.uint16).numpy(), bs)
+    got = C.float().cpu().numpy()
+    # BF16 tolerance of the path: 1e-2 relative, measured against the size of the accumulated terms
+    scale = np.abs(f32) + 1e-2 * np.sqrt((np.diff(a.block_row_ptr.numpy()).repeat(bs) * bs)[:, None] + 1.0)
+    assert np.all(np.abs(got - f32) <= 1e-2 * scale), float(np.max(np.abs(got - f32) / scale))
+    return got, bits
+
+
+@pytest.mark.parametrize("bs", [4, 8, 16, 32])
+def test_bsr_bf16(ctx, bs):
+    _bsr_bf16_case(ctx, 24, 20, bs, 24, 0.25, seed=bs)
+
+
+@pytest.mark.parametrize("n", [8, 64, 128, 200, 512])
+def test_bsr16_bf16_shapes(ctx, n):
+    """16 x 16 blocks (the tensor-core path), with empty block rows and ragged N."""
+    _bsr_bf16_case(ctx, 48, 40, 16, n, 0.08, seed=n)
+
+
+def test_config_c5_reduced(ctx):
+    a, B = W.config_c5(device="cuda", block_grid=256, n_rhs=512)
+    C = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, B, 16)
+    bits, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.cpu().numpy(), a.block_col_idx.cpu().numpy(),
+                                     a.block_values.view(torch.uint16).cpu().numpy(),
+                                     B.view(torch.uint16).cpu().numpy(), 16)
+    got = C.float().cpu().numpy()
+    scale = np.abs(f32) + 1e-2 * np.sqrt(np.diff(a.block_row_ptr.cpu().numpy()).repeat(16) * 16 + 1.0)[:, None]
+    assert np.all(np.abs(got - f32) <= 1e-2 * scale)
