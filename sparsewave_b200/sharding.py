@@ -1,0 +1,124 @@
+"""Row sharding of one CSR / BSR operator over the GPUs of one node.
+
+Not a reference feature (the reference is single GPU).  Rows are cut into
+contiguous shards balanced by nnz (`swb_shard_rows_by_nnz`); rank k keeps the
+row offsets of its rows rebased to zero, its slice of the column indices and
+values, global column numbering, and the matching rows of the output.  The
+dense operand (x for SpMV, B for SpMM) is owned in equal contiguous row chunks
+and gathered into every rank's own full copy with one NCCL all-gather before
+the local kernel runs; outputs stay sharded.
+
+One process per GPU; `torch.distributed` is the plumbing (NCCL on GPUs, gloo in
+the CPU tests of this host logic).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import api
+
+
+def dense_chunk(n_rows: int, world: int) -> int:
+    """Rows of the dense operand owned by each rank: ceil(n_rows / world); rank k
+    owns [k * chunk, min((k + 1) * chunk, n_rows))."""
+    return -(-n_rows // world)
+
+
+def owned_dense_range(n_rows: int, world: int, rank: int) -> tuple[int, int]:
+    c = dense_chunk(n_rows, world)
+    return min(rank * c, n_rows), min((rank + 1) * c, n_rows)
+
+
+@dataclass
+class CsrShard:
+    """Rows [row_begin, row_end) of a CSR matrix, offsets rebased to zero."""
+    rank: int
+    world: int
+    rows_total: int
+    cols: int
+    row_begin: int
+    row_end: int
+    row_ptr: torch.Tensor
+    col_idx: torch.Tensor
+    values: torch.Tensor
+
+    @property
+    def rows(self) -> int:
+        return self.row_end - self.row_begin
+
+    @property
+    def nnz(self) -> int:
+        return int(self.values.numel())
+
+
+def shard_boundaries(row_ptr, world: int) -> np.ndarray:
+    """nnz-balanced row boundaries (world + 1 entries) from the full row offsets."""
+    if isinstance(row_ptr, torch.Tensor):
+        row_ptr = row_ptr.cpu().numpy()
+    return api.shard_rows_by_nnz(row_ptr, world)
+
+
+def shard_csr(row_ptr: torch.Tensor, col_idx: torch.Tensor, values: torch.Tensor, cols: int, rank: int,
+              world: int, boundaries: Optional[np.ndarray] = None) -> CsrShard:
+    """Cuts rank's shard out of the full matrix (tensors on any device)."""
+    rows_total = int(row_ptr.numel() - 1)
+    if boundaries is None:
+        boundaries = shard_boundaries(row_ptr, world)
+    r0, r1 = int(boundaries[rank]), int(boundaries[rank + 1])
+    p0, p1 = int(row_ptr[r0]), int(row_ptr[r1])
+    local_ptr = (row_ptr[r0:r1 + 1] - p0).to(torch.int32).contiguous()
+    return CsrShard(rank, world, rows_total, cols, r0, r1, local_ptr, col_idx[p0:p1].contiguous(),
+                    values[p0:p1].contiguous())
+
+
+def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
+    """Gathers every rank's chunk of the dense operand (leading dimension split
+    by `dense_chunk`) into a full copy on this rank; returns its first n_rows rows."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    chunk = dense_chunk(n_rows, world)
+    tail = tuple(owned.shape[1:])
+    if out is None:
+        out = torch.empty((chunk * world,) + tail, dtype=owned.dtype, device=owned.device)
+    if world == 1:
+        out[:owned.shape[0]].copy_(owned)
+        return out[:n_rows]
+    send = owned
+    if owned.shape[0] != chunk:  # the last rank's chunk may be short: pad to the common size
+        send = torch.zeros((chunk,) + tail, dtype=owned.dtype, device=owned.device)
+        send[:owned.shape[0]].copy_(owned)
+    dist.all_gather_into_tensor(out.view(-1), send.contiguous().view(-1), group=group)
+    return out[:n_rows]
+
+
+class ShardedOperator:
+    """A row shard bound to a library context: gathers the dense operand, then
+    runs the local kernel on this rank's rows."""
+
+    def __init__(self, ctx: api.Context, shard: CsrShard, options, group=None):
+        self.ctx, self.shard, self.options, self.group = ctx, shard, options, group
+        self._full = None
+
+    def _gather(self, owned: torch.Tensor, n_rows: int) -> torch.Tensor:
+        world = self.shard.world
+        chunk = dense_chunk(n_rows, world)
+        shape = (chunk * world,) + tuple(owned.shape[1:])
+        if self._full is None or tuple(self._full.shape) != shape or self._full.dtype != owned.dtype:
+            self._full = torch.empty(shape, dtype=owned.dtype, device=owned.device)
+        return allgather_dense(owned, n_rows, self._full, self.group)
+
+    def spmv(self, x_owned: torch.Tensor, y_local: Optional[torch.Tensor] = None, *, replicated_x=None):
+        """y[row_begin:row_end] = A_shard @ x.  `x_owned` is this rank's chunk of x;
+        pass `replicated_x` instead when every rank already holds all of x."""
+        s = self.shard
+        x = replicated_x if replicated_x is not None else self._gather(x_owned, s.cols)
+        return self.ctx.spmv(self.options, s.row_ptr, s.col_idx, s.values, x, y_local, rows=s.rows)
+
+    def spmm(self, B_owned: torch.Tensor, C_local: Optional[torch.Tensor] = None, *, replicated_B=None):
+        s = self.shard
+        B = replicated_B if replicated_B is not None else self._gather(B_owned, s.cols)
+        return self.ctx.spmm(self.options, s.row_ptr, s.col_idx, s.values, B, C_local, rows=s.rows)

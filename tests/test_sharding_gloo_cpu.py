@@ -1,0 +1,76 @@
+"""Host logic of the multi-GPU path on CPU: two gloo ranks cut nnz-balanced row
+shards, all-gather the dense operand and together reproduce the one-rank result.
+(The local arithmetic here is the oracle: this test covers sharding and the
+exchange step, not the kernels.)"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from sparsewave_b200 import sharding
+from tests.helpers import random_csr
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows, cols = 1203, 701  # cols not divisible by the world size
+        rp, ci, v = random_csr(rows, cols, 9, seed=21, empty_fraction=0.3)
+        x = np.random.default_rng(21).uniform(-1, 1, cols).astype(np.float32)
+        B = np.random.default_rng(22).uniform(-1, 1, (cols, 3)).astype(np.float32)
+        shard = sharding.shard_csr(torch.from_numpy(rp), torch.from_numpy(ci), torch.from_numpy(v), cols, rank, world)
+        lo, hi = sharding.owned_dense_range(cols, world, rank)
+        x_full = sharding.allgather_dense(torch.from_numpy(x[lo:hi].copy()), cols)
+        B_full = sharding.allgather_dense(torch.from_numpy(B[lo:hi].copy()), cols)
+        assert np.array_equal(x_full.numpy(), x) and np.array_equal(B_full.numpy(), B)
+        y = oracle.csr_spmv(shard.row_ptr.numpy(), shard.col_idx.numpy(), shard.values.numpy(), x_full.numpy())
+        C = oracle.csr_spmm(shard.row_ptr.numpy(), shard.col_idx.numpy(), shard.values.numpy(), B_full.numpy())
+        assert np.array_equal(y, oracle.csr_spmv(rp, ci, v, x)[shard.row_begin:shard.row_end])
+        assert np.array_equal(C, oracle.csr_spmm(rp, ci, v, B)[shard.row_begin:shard.row_end])
+        results[rank] = (shard.row_begin, shard.row_end, shard.nnz)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_spmv_spmm():
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
+        r = dict(results)
+    assert r[0][0] == 0 and r[0][1] == r[1][0] and r[1][1] == 1203
+    total = r[0][2] + r[1][2]
+    assert abs(r[0][2] - total / 2) <= 64  # nnz-balanced up to one row
+
+
+def test_boundaries_are_deterministic_and_cover_rows():
+    rp, _, _ = random_csr(5000, 100, 12, seed=5)
+    for world in (1, 2, 4, 8):
+        b = sharding.shard_boundaries(torch.from_numpy(rp), world)
+        assert b[0] == 0 and b[-1] == 5000 and np.all(np.diff(b) >= 0)
+        assert np.array_equal(b, sharding.shard_boundaries(rp, world))
+        nnz = np.diff(rp[b])
+        assert nnz.max() - nnz.min() <= 2 * np.diff(rp).max()
+    # one indivisible long row
+    rp = np.array([0, 1, 1000, 1001, 1002], np.int32)
+    b = sharding.shard_boundaries(rp, 4)
+    assert b[0] == 0 and b[-1] == 4 and np.all(np.diff(b) >= 0)
+
+
+def test_dense_chunks():
+    assert sharding.dense_chunk(701, 2) == 351
+    assert sharding.owned_dense_range(701, 2, 1) == (351, 701)
+    assert sharding.owned_dense_range(5, 8, 7) == (5, 5)
