@@ -282,8 +282,8 @@ __device__ __forceinline__ int warp_row_search(const int32_t *__restrict__ row_p
   return lo - 1;
 }
 
-template <bool TRACE>
-__global__ void spmv_wave_per_position_kernel(int64_t rows, int64_t nnz, int64_t wave_count,
+template <bool TRACE, int MAX_BLOCK>
+__global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_per_position_kernel(int64_t rows, int64_t nnz, int64_t wave_count,
                                               int64_t batch, const int32_t *__restrict__ row_ptr,
                                               const int32_t *__restrict__ col,
                                               const float *__restrict__ val,
@@ -547,12 +547,16 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   const int64_t grid = wave_per_position_physical_grid(a.nnz, block, batch);
   if (physical_grid) *physical_grid = grid;
   const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
-  if (trace.enabled())
-    spmv_wave_per_position_kernel<true><<<(unsigned)grid, block, smem, s>>>(
-        a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
-  else
-    spmv_wave_per_position_kernel<false><<<(unsigned)grid, block, smem, s>>>(
-        a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+  // Blocks above 512 threads need the register-capped instantiation.
+#define SWB_WPP(TR, MB)                                                                   \
+  spmv_wave_per_position_kernel<TR, MB><<<(unsigned)grid, block, smem, s>>>(               \
+      a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace)
+  if (trace.enabled()) {
+    if (block > 512) SWB_WPP(true, 1024); else SWB_WPP(true, 512);
+  } else {
+    if (block > 512) SWB_WPP(false, 1024); else SWB_WPP(false, 512);
+  }
+#undef SWB_WPP
   ++*launches;
   return cudaGetLastError();
 }
