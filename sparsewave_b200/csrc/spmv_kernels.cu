@@ -452,6 +452,8 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_per_position_kernel(int64
   }
 }
 
+#include "spmv_wave_span.cuh"
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline unsigned grid_of(int64_t blocks) { return (unsigned)max1(blocks); }
@@ -528,7 +530,6 @@ int64_t wave_per_position_auto_batch(int64_t nnz, int block, const DeviceInfo &d
   int64_t batch = waves / target_warps;
   if (batch < 1) batch = 1;
   if (batch > 64) batch = 64;
-  if (batch > TILE_WAVES) batch -= batch % TILE_WAVES;
   return batch;
 }
 
@@ -547,10 +548,21 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   const int64_t grid = wave_per_position_physical_grid(a.nnz, block, batch);
   if (physical_grid) *physical_grid = grid;
   const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
-  // Blocks above 512 threads need the register-capped instantiation.
+  // Spans of two or more partitions take the chunked span kernel (needs
+  // 16-byte aligned col/val); batch == 1 is the reference schedule, one
+  // partition per warp and lane == position.  Blocks above 512 threads need
+  // the register-capped instantiation.
+  const bool span = batch >= 2 && aligned16(a.col_idx) && aligned16(a.val);
+  const size_t span_smem = (size_t)(block / 32) * SPAN_CHUNK * sizeof(int);
 #define SWB_WPP(TR, MB)                                                                   \
-  spmv_wave_per_position_kernel<TR, MB><<<(unsigned)grid, block, smem, s>>>(               \
-      a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace)
+  do {                                                                                    \
+    if (span)                                                                             \
+      spmv_wave_span_kernel<TR, MB><<<(unsigned)grid, block, span_smem, s>>>(              \
+          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);      \
+    else                                                                                  \
+      spmv_wave_per_position_kernel<TR, MB><<<(unsigned)grid, block, smem, s>>>(           \
+          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);      \
+  } while (0)
   if (trace.enabled()) {
     if (block > 512) SWB_WPP(true, 1024); else SWB_WPP(true, 512);
   } else {
