@@ -118,6 +118,13 @@ SWB_API const char *swb_version(void);
 /* Number of kernels this context has launched since creation. */
 SWB_API int64_t swb_kernel_launch_count(const swb_context *ctx);
 
+/* Reads the context's device status word after the work queued on `stream`
+ * has finished (synchronises that stream).  0 means no kernel gave up one of
+ * its bounded waits; non-zero means a tensor-core BSR kernel abandoned a wait
+ * on its pipeline barriers and its output is not valid. */
+SWB_API int swb_device_status(swb_context *ctx, swb_stream stream,
+                              int32_t *status);
+
 /* ---- options (replaces the pass / pipeline option parsing) -------------- */
 
 SWB_API void swb_options_default(swb_options *opts);

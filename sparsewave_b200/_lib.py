@@ -71,6 +71,7 @@ SIGNATURES = {
     "swb_last_error": (C.c_char_p, [_CTX]),
     "swb_version": (C.c_char_p, []),
     "swb_kernel_launch_count": (_I64, [_CTX]),
+    "swb_device_status": (C.c_int, [_CTX, _P, C.POINTER(C.c_int32)]),
     "swb_options_default": (None, [_OPT]),
     "swb_options_parse": (C.c_int, [_CTX, _OPT, C.c_char_p]),
     "swb_options_validate": (C.c_int, [_CTX, _OPT]),

@@ -117,6 +117,12 @@ class Context:
     def kernel_launches(self) -> int:
         return int(self._lib.swb_kernel_launch_count(self._ctx))
 
+    def device_status(self) -> int:
+        """Status word of kernels with bounded waits (synchronises the current stream); 0 = healthy."""
+        v = C.c_int32(-1)
+        self._check(self._lib.swb_device_status(self._ctx, self._stream(), C.byref(v)))
+        return int(v.value)
+
     def validate(self, options) -> None:
         self._check(self._lib.swb_options_validate(self._ctx, C.byref(self._opts(options))))
 

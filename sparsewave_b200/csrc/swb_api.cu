@@ -160,7 +160,26 @@ int swb_create(swb_context **out_ctx, int device_ordinal) {
   ctx->device = device_ordinal;
   cudaDeviceGetAttribute(&ctx->dev.sm_count, cudaDevAttrMultiProcessorCount, device_ordinal);
   cudaDeviceGetAttribute(&ctx->dev.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_ordinal);
+  // Status word of kernels with bounded waits (0 = no wait ever gave up).
+  e = cudaMalloc(&ctx->status_flag, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->status_flag, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    delete ctx;
+    return cuda_fail(nullptr, e, "cudaMalloc(status)");
+  }
   *out_ctx = ctx;
+  return SWB_OK;
+}
+
+int swb_device_status(swb_context *ctx, swb_stream stream, int32_t *status) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (!status) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "status is NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  SWB_CUDA(ctx, cudaMemcpyAsync(&v, ctx->status_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+  SWB_CUDA(ctx, cudaStreamSynchronize(s));
+  *status = v;
   return SWB_OK;
 }
 
@@ -569,7 +588,11 @@ int swb_bsr_spmm_bf16(swb_context *ctx, const swb_options *o, int64_t rows, int6
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: NULL operand pointer");
   swb::BsrSpmmArgs a{rows, cols, nnzb, bs, n_rhs, brp, bci, bv, B, C};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t e = swb::launch_bsr_spmm_thread_per_output_bf16(a, (int)o->spmm_block_size, s, &ctx->launches);
+  cudaError_t e;
+  if (swb::bsr16_tcgen05_supported(a))
+    e = swb::launch_bsr16_spmm_tcgen05(a, ctx->status_flag, ctx->dev, s, &ctx->launches);
+  else
+    e = swb::launch_bsr_spmm_thread_per_output_bf16(a, (int)o->spmm_block_size, s, &ctx->launches);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "bsr_spmm launch");
   return SWB_OK;
 }

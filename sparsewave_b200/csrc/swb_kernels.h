@@ -94,6 +94,7 @@ cudaError_t launch_bsr_spmm_thread_per_output_bf16(const BsrSpmmArgs &a,
                                                    int64_t *launches);
 // 16x16 bf16 blocks on the tcgen05 tensor cores.  `status_flag` is a device
 // int the kernel sets non-zero when one of its bounded waits gives up.
+bool bsr16_tcgen05_supported(const BsrSpmmArgs &a);
 cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag,
                                       const DeviceInfo &dev, cudaStream_t s,
                                       int64_t *launches);

@@ -117,7 +117,7 @@ def _bsr_bf16_case(ctx, grid_rows, grid_cols, bs, n, density, seed):
     a = W.random_bsr(grid_rows, grid_cols, bs, density, seed=seed)
     B = W.dense_normal((grid_cols * bs, n), seed=seed)
     C = ctx.bsr_spmm("", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(), B.cuda(), bs)
-    torch.cuda.synchronize()
+    assert ctx.device_status() == 0  # no bounded wait of the tensor-core kernel gave up
     bits, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.numpy(), a.block_col_idx.numpy(),
                                      a.block_values.view(torch.uint16).numpy(), B.view(torch.uint16).numpy(), bs)
     got = C.float().cpu().numpy()
@@ -141,6 +141,7 @@ def test_bsr16_bf16_shapes(ctx, n):
 def test_config_c5_reduced(ctx):
     a, B = W.config_c5(device="cuda", block_grid=256, n_rhs=512)
     C = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, B, 16)
+    assert ctx.device_status() == 0
     bits, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.cpu().numpy(), a.block_col_idx.cpu().numpy(),
                                      a.block_values.view(torch.uint16).cpu().numpy(),
                                      B.view(torch.uint16).cpu().numpy(), 16)
