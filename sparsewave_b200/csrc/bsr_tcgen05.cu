@@ -130,9 +130,16 @@ __global__ void __launch_bounds__(128) bsr16_spmm_tcgen05_kernel(
     const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
     const int first = start + c * CHUNK;
     const int count = min(CHUNK, end - first);
-    for (int j = 0; j < count; ++j) {
+    // Block-column indices of the whole chunk first (independent loads), so that
+    // the copies below do not wait for one index load per block.
+    int bcs[CHUNK];
+#pragma unroll
+    for (int j = 0; j < CHUNK; ++j) bcs[j] = (j < count) ? __ldg(bci + first + j) : 0;
+#pragma unroll
+    for (int j = 0; j < CHUNK; ++j) {
+      if (j >= count) break;
       const int bp = first + j;
-      const int64_t bc = __ldg(bci + bp);
+      const int64_t bc = bcs[j];
       const uint32_t item = sbase + (uint32_t)j * ITEM_BYTES;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {

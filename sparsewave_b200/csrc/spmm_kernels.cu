@@ -52,9 +52,9 @@ __global__ void spmm_thread_per_output_kernel(int64_t rows, int64_t N,
 // for the T right-hand-side columns of the tile.  A tile that reaches past N
 // runs the guarded path.
 //
-// TCAP is T rounded up to a power of two.  When T == TCAP, T % 4 == 0,
-// N % 4 == 0 and B, C are 16-byte aligned, the T floats of a B row are read
-// with 128-bit loads and the result is written with 128-bit stores.
+// TCAP is T rounded up to a power of two (columns k >= T are inactive).  Full
+// tiles of 4, 8, 16 or 32 columns on 16-byte aligned operands take the
+// vectorised kernel further below instead.
 //
 // Reduction: instead of T independent 5-step butterflies (5*T shuffles) the
 // warp does a halving exchange: at the step with lane distance `off` each
@@ -115,7 +115,7 @@ __device__ __forceinline__ bool lane_is_column_writer(int lane) {
   return (lane & ~used) == 0;
 }
 
-template <int TCAP, bool VEC>
+template <int TCAP>
 __global__ void spmm_wave_per_row_tile_kernel(int64_t rows, int64_t N, int T, int64_t tiles,
                                               const int32_t *__restrict__ row_ptr,
                                               const int32_t *__restrict__ col,
@@ -133,21 +133,7 @@ __global__ void spmm_wave_per_row_tile_kernel(int64_t rows, int64_t N, int T, in
 #pragma unroll
   for (int k = 0; k < TCAP; ++k) acc[k] = 0.0f;
 
-  if (VEC) {  // implies T == TCAP, full tiles only, aligned
-    for (int p = start + lane; p < end; p += 32) {
-      const int c = __ldcs(col + p);
-      const float v = __ldcs(val + p);
-      const float4 *b4 = reinterpret_cast<const float4 *>(B + (int64_t)c * N + j0);
-#pragma unroll
-      for (int q = 0; q < TCAP / 4; ++q) {
-        const float4 b = __ldg(b4 + q);
-        acc[4 * q + 0] = add(acc[4 * q + 0], mul(v, b.x));
-        acc[4 * q + 1] = add(acc[4 * q + 1], mul(v, b.y));
-        acc[4 * q + 2] = add(acc[4 * q + 2], mul(v, b.z));
-        acc[4 * q + 3] = add(acc[4 * q + 3], mul(v, b.w));
-      }
-    }
-  } else if (full && T == TCAP) {
+  if (full && T == TCAP) {
     for (int p = start + lane; p < end; p += 32) {
       const int c = __ldcs(col + p);
       const float v = __ldcs(val + p);
@@ -170,6 +156,67 @@ __global__ void spmm_wave_per_row_tile_kernel(int64_t rows, int64_t N, int T, in
   tile_reduce<TCAP>(acc, lane);
   const int k = tile_column_of_lane<TCAP>(lane);
   if (lane_is_column_writer<TCAP>(lane) && k < T && j0 + k < N) C[row * N + j0 + k] = acc[0];
+}
+
+// Full tiles of 4, 8, 16 or 32 columns with 16-byte aligned B and C rows.  The
+// unit <-> (row, tile) assignment is the same; inside the warp G = T/4 adjacent
+// lanes share a position and read the tile's T floats of that B row as one
+// contiguous run of G float4 (64 contiguous bytes per position for T = 16), and
+// the 32/G lane groups stride the row's positions.  Each lane keeps one float4
+// of partial sums.  Reduction over the lane groups: two halving exchanges (lane
+// distance 16 keeps two of the four components, distance 8 keeps one), then
+// plain butterfly steps down to distance G: 3 + log2(8/G) shuffles.
+template <int G>
+__global__ void spmm_wave_per_row_tile_vec_kernel(int64_t rows, int64_t N, int64_t tiles,
+                                                  const int32_t *__restrict__ row_ptr,
+                                                  const int32_t *__restrict__ col,
+                                                  const float *__restrict__ val,
+                                                  const float *__restrict__ B, float *__restrict__ C) {
+  constexpr int T = 4 * G, PG = 32 / G;
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * tiles) return;
+  const int64_t row = unit / tiles;
+  const int64_t j0 = (unit % tiles) * T;
+  const int cq = lane % G, pg = lane / G;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  const float *Bt = B + j0 + 4 * cq;
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int p = start + pg;
+  for (; p + PG < end; p += 2 * PG) {
+    const int c0 = __ldg(col + p), c1 = __ldg(col + p + PG);
+    const float v0 = __ldg(val + p), v1 = __ldg(val + p + PG);
+    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+    const float4 b1 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c1 * N));
+    acc.x = add(acc.x, mul(v0, b0.x)); acc.y = add(acc.y, mul(v0, b0.y));
+    acc.z = add(acc.z, mul(v0, b0.z)); acc.w = add(acc.w, mul(v0, b0.w));
+    acc.x = add(acc.x, mul(v1, b1.x)); acc.y = add(acc.y, mul(v1, b1.y));
+    acc.z = add(acc.z, mul(v1, b1.z)); acc.w = add(acc.w, mul(v1, b1.w));
+  }
+  if (p < end) {
+    const int c0 = __ldg(col + p);
+    const float v0 = __ldg(val + p);
+    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+    acc.x = add(acc.x, mul(v0, b0.x)); acc.y = add(acc.y, mul(v0, b0.y));
+    acc.z = add(acc.z, mul(v0, b0.z)); acc.w = add(acc.w, mul(v0, b0.w));
+  }
+
+  // distance 16: lanes with bit 4 set keep (z, w), the others (x, y)
+  const bool up16 = (lane & 16) != 0;
+  float k0 = up16 ? acc.z : acc.x, k1 = up16 ? acc.w : acc.y;
+  const float s0 = up16 ? acc.x : acc.z, s1 = up16 ? acc.y : acc.w;
+  k0 = add(k0, __shfl_xor_sync(FULL, s0, 16));
+  k1 = add(k1, __shfl_xor_sync(FULL, s1, 16));
+  // distance 8: lanes with bit 3 set keep the second of the two
+  const bool up8 = (lane & 8) != 0;
+  float r = up8 ? k1 : k0;
+  const float s = up8 ? k0 : k1;
+  r = add(r, __shfl_xor_sync(FULL, s, 8));
+#pragma unroll
+  for (int off = 4; off >= G; off >>= 1) r = add(r, __shfl_xor_sync(FULL, r, off));
+  const int comp = (up16 ? 2 : 0) + (up8 ? 1 : 0);
+  if ((lane & 7 & ~(G - 1)) == 0) C[row * N + j0 + 4 * cq + comp] = r;
 }
 
 // ---------------------------------------------------------------------------
@@ -222,10 +269,10 @@ cudaError_t launch_tile(const CsrSpmmArgs &a, int block, int T, cudaStream_t s) 
                    aligned16(a.B) && aligned16(a.C);
   if (vec) {
     if constexpr (TCAP >= 4)
-      spmm_wave_per_row_tile_kernel<TCAP, true><<<grid, block, 0, s>>>(
-          a.rows, a.n_rhs, T, tiles, a.row_ptr, a.col_idx, a.val, a.B, a.C);
+      spmm_wave_per_row_tile_vec_kernel<TCAP / 4><<<grid, block, 0, s>>>(a.rows, a.n_rhs, tiles, a.row_ptr,
+                                                                          a.col_idx, a.val, a.B, a.C);
   } else {
-    spmm_wave_per_row_tile_kernel<TCAP, false><<<grid, block, 0, s>>>(
+    spmm_wave_per_row_tile_kernel<TCAP><<<grid, block, 0, s>>>(
         a.rows, a.n_rhs, T, tiles, a.row_ptr, a.col_idx, a.val, a.B, a.C);
   }
   return cudaGetLastError();
