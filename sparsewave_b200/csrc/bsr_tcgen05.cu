@@ -1,4 +1,5 @@
-// BSR SpMM for 16x16 bf16 blocks on the Blackwell tensor cores (tcgen05 + TMEM).
+// BSR SpMM for 16x16 bf16 blocks on the Blackwell tensor cores:
+// TMA (cp.async.bulk.tensor) -> shared memory -> tcgen05.mma -> TMEM -> tcgen05.ld.
 //
 // Reference arithmetic (ThreadPerOutputBSRSpMMPattern, SparseWaveToGPU.cpp:560-665):
 //   C[br*16 + r, j] = sum over blocks bp of block row br, sum over lc:
@@ -11,19 +12,29 @@
 //   D[m, r] (+)= sum_k  Bt[m, k] * At[k, r],   m = column in the tile, k = lc,
 // one tcgen05.mma of shape M=128, N=16, K=16 per nonzero block, all blocks of
 // the block row accumulating into one 128-lane x 16-column f32 tile in TMEM.
-//   - MMA operand A = the 16 x 128 slab B[bci*16 .. +16, n0 .. n0+128): row k is
-//     contiguous in memory along m, i.e. MN-major.
-//   - MMA operand B = the block itself, [r][lc] row-major: K-major.
-// Both operands are staged in shared memory in the canonical no-swizzle layouts
-// of 8 x 16-byte core matrices by 16-byte cp.async copies (the slab rows are
-// gathered by block-column index, so there is no dense tile for a bulk tensor
-// copy to fetch), double-buffered in chunks of CHUNK blocks.  One thread issues
-// the MMAs; tcgen05.commit signals an mbarrier when a chunk's MMAs have read
-// their operands.  The epilogue reads the accumulator with tcgen05.ld (each of
-// the four warps its own 32 TMEM lanes), rounds to bf16 and stores C.
+//   - MMA operand A = the 16 x 128 slab B[bci*16 .. +16, n0 .. n0+128).  Row k
+//     is contiguous along m: MN-major.  Two TMA boxes of 64 columns x 16 rows
+//     with the 128-byte swizzle land it as the canonical MN-major SWIZZLE_128B
+//     layout (128-byte rows, 1024 bytes between groups of 8 k rows = stride
+//     byte offset, 2048 bytes between the two 64-column halves = leading byte
+//     offset).  Columns past N are zero-filled by the TMA unit.
+//   - MMA operand B = the block itself, [r][lc] row-major: K-major.  One TMA box
+//     of 16 x 16 with the 32-byte swizzle over the block values viewed as a
+//     (nnzb*16) x 16 matrix lands it as the canonical K-major SWIZZLE_32B layout
+//     (32-byte rows, 256 bytes between groups of 8 rows = stride byte offset).
+// The slab rows are gathered by block-column index, one box pair per block.
 //
-// Every mbarrier wait is bounded: when it runs out the kernel raises the status
-// flag, drains its copies, frees its TMEM columns and returns.
+// Pipeline.  One thread is both producer and MMA issuer: it arms a stage's
+// `full` mbarrier with the byte count, issues the stage's TMA copies, and
+// STAGES-1 chunks later waits for that barrier and issues the chunk's MMAs;
+// tcgen05.commit arrives on the stage's `empty` mbarrier when the MMAs have
+// read their operands.  After the last chunk a commit arrives on `done`; the
+// four warps then read the accumulator with tcgen05.ld (each its own 32 TMEM
+// lanes), round to bf16 and store C.
+//
+// Every mbarrier wait is bounded: when one runs out the kernel raises the
+// status word, frees its TMEM columns and returns.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "swb_index.h"
@@ -33,36 +44,37 @@ namespace swb {
 namespace {
 
 constexpr int TILE_N = 128;                  // right-hand-side columns per CTA (MMA M)
-constexpr int CHUNK = 8;                     // blocks per pipeline stage
-constexpr int STAGES = 2;
+constexpr int CHUNK = 4;                     // blocks per pipeline stage
+constexpr int STAGES = 4;
 constexpr int SLAB_BYTES = 16 * TILE_N * 2;  // 4096: one 16 x 128 bf16 slab
+constexpr int HALF_SLAB = SLAB_BYTES / 2;    // 2048: 64 columns x 16 rows
 constexpr int BLOCK_BYTES = 16 * 16 * 2;     // 512
-constexpr int ITEM_BYTES = SLAB_BYTES + BLOCK_BYTES;
-constexpr int STAGE_BYTES = CHUNK * ITEM_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128;  // + alignment slack
+constexpr int STAGE_SLABS = CHUNK * SLAB_BYTES;
+constexpr int STAGE_BYTES = STAGE_SLABS + CHUNK * BLOCK_BYTES;  // slabs first (1024-aligned), then blocks
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;         // + alignment slack
 constexpr int TMEM_COLS = 32;                // minimum allocation; 16 are used
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int PRODUCER_THREAD = 128;         // lane 0 of a fifth warp issues TMA and MMA
+constexpr int THREADS = 160;
+static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled slabs");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-// Shared-memory matrix descriptor, no swizzle, version 1 (Blackwell):
-// bits [0,14) address >> 4, [16,30) leading byte offset >> 4, [32,46) stride
-// byte offset >> 4, [46,48) version, [61,64) layout type (0 = no swizzle).
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor, version 1 (Blackwell): bits [0,14) address
+// >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) version, [61,64) layout type (2 = 128-byte swizzle, 6 = 32-byte).
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout) {
   return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
 
 // Instruction descriptor for kind::f16: D f32 (bits 4-5 = 1), A and B bf16
 // (bits 7-9 and 10-12 = 1), A MN-major (bit 15), B K-major (bit 16 = 0),
 // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -79,34 +91,48 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
-__global__ void __launch_bounds__(128) bsr16_spmm_tcgen05_kernel(
-    int64_t n_tiles, int64_t N, const int32_t *__restrict__ brp, const int32_t *__restrict__ bci,
-    const __nv_bfloat16 *__restrict__ bv, const __nv_bfloat16 *__restrict__ B, __nv_bfloat16 *__restrict__ C,
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_B, const __grid_constant__ CUtensorMap map_A, int64_t n_tiles,
+    int64_t N, const int32_t *__restrict__ brp, const int32_t *__restrict__ bci, __nv_bfloat16 *__restrict__ C,
     int *status) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t mbar[STAGES];
+  __shared__ __align__(8) uint64_t bar_full[STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[STAGES];
+  __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t br = blockIdx.x / n_tiles;
-  const int64_t n0 = (blockIdx.x % n_tiles) * TILE_N;
-  const uint32_t stage0 = (smem_u32(smem_raw) + 127u) & ~127u;
+  const int n0 = (int)((blockIdx.x % n_tiles) * TILE_N);
+  const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int start = brp[br], end = brp[br + 1];
   const int nblk = end - start;
 
   if (nblk == 0) {  // empty block row: C = 0
-    const int64_t col = n0 + tid;
-    if (col < N)
+    const int64_t col = (int64_t)n0 + tid;
+    if (tid < TILE_N && col < N)
       for (int r = 0; r < 16; ++r) C[(br * 16 + r) * N + col] = __float2bfloat16_rn(0.0f);
     return;
   }
 
   if (tid == 0) {
     failed = 0;
-    for (int s = 0; s < STAGES; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[s])) : "memory");
+    for (int s = 0; s < STAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_full[s])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_empty[s])) : "memory");
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_done)) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_B) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_A) : "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
@@ -119,102 +145,74 @@ __global__ void __launch_bounds__(128) bsr16_spmm_tcgen05_kernel(
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_slot;
 
-  // cp.async copies of chunk c into stage s.  Slab unit u (16 bytes) of a
-  // block: ki = u % 8 (k within its group of 8), mg = (u / 8) % 16 (group of 8
-  // columns), kg = u / 128; it lands at byte u * 16, which is the canonical
-  // layout with 16 B between k rows, 128 B between column groups (stride byte
-  // offset) and 2048 B between k groups (leading byte offset).  Block unit g
-  // (row r = g / 2, k half kc = g % 2) lands at (kc * 16 + r) * 16: 16 B between
-  // rows, 128 B between row groups (SBO), 256 B between k halves (LBO).
-  auto issue_loads = [&](int c, int s) {
-    const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
-    const int first = start + c * CHUNK;
-    const int count = min(CHUNK, end - first);
-    // Block-column indices of the whole chunk first (independent loads), so that
-    // the copies below do not wait for one index load per block.
-    int bcs[CHUNK];
+  if (tid == PRODUCER_THREAD) {
+    const int nchunks = (nblk + CHUNK - 1) / CHUNK;
+    bool ok = true;
+    // Iteration i produces chunk i (if any) and consumes chunk i - (STAGES-1).
+    for (int i = 0; i < nchunks + STAGES - 1 && ok; ++i) {
+      if (i < nchunks) {
+        const int s = i % STAGES;
+        if (i >= STAGES) {  // the MMAs of chunk i - STAGES must have read this stage
+          ok = mbar_wait(smem_u32(&bar_empty[s]), ((i / STAGES) - 1) & 1u);
+          if (!ok) break;
+        }
+        const int first = start + i * CHUNK;
+        const int count = min(CHUNK, end - first);
+        int bcs[CHUNK];
 #pragma unroll
-    for (int j = 0; j < CHUNK; ++j) bcs[j] = (j < count) ? __ldg(bci + first + j) : 0;
+        for (int j = 0; j < CHUNK; ++j) bcs[j] = (j < count) ? __ldg(bci + first + j) : 0;
+        const uint32_t full = smem_u32(&bar_full[s]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full),
+                     "r"((uint32_t)count * (SLAB_BYTES + BLOCK_BYTES))
+                     : "memory");
+        const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
 #pragma unroll
-    for (int j = 0; j < CHUNK; ++j) {
-      if (j >= count) break;
-      const int bp = first + j;
-      const int64_t bc = bcs[j];
-      const uint32_t item = sbase + (uint32_t)j * ITEM_BYTES;
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int u = tid + 128 * i;
-        const int ki = u & 7, mg = (u >> 3) & 15, kg = u >> 7;
-        const int64_t col = n0 + mg * 8;
-        const bool ok = col < N;
-        const __nv_bfloat16 *src = ok ? B + (bc * 16 + kg * 8 + ki) * N + col : B;
-        cp_async16(item + (uint32_t)u * 16, src, ok ? 16u : 0u);
+        for (int j = 0; j < CHUNK; ++j) {
+          if (j >= count) break;
+          const uint32_t slab = sbase + (uint32_t)j * SLAB_BYTES;
+          tma_load_2d(slab, &map_B, n0, bcs[j] * 16, full);
+          tma_load_2d(slab + HALF_SLAB, &map_B, n0 + 64, bcs[j] * 16, full);
+          tma_load_2d(sbase + STAGE_SLABS + (uint32_t)j * BLOCK_BYTES, &map_A, 0, (first + j) * 16, full);
+        }
       }
-      if (tid < 32) {
-        const int r = tid >> 1, kc = tid & 1;
-        cp_async16(item + SLAB_BYTES + (uint32_t)(kc * 16 + r) * 16, bv + (int64_t)bp * 256 + tid * 8, 16u);
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-
-  const int nchunks = (nblk + CHUNK - 1) / CHUNK;
-  uint32_t uses[STAGES] = {0, 0};  // completed waits per stage -> wait parity
-  bool ok = true;
-
-  issue_loads(0, 0);
-  for (int c = 0; c < nchunks && ok; ++c) {
-    const int s = c & 1;
-    if (c + 1 < nchunks) {
-      if (c >= 1) {  // stage s^1 still feeds the MMAs of chunk c-1
-        ok = mbar_wait(smem_u32(&mbar[s ^ 1]), uses[s ^ 1] & 1u);
-        uses[s ^ 1]++;
-        ok = __syncthreads_and(ok);  // one decision for the whole CTA
+      const int c = i - (STAGES - 1);
+      if (c >= 0) {
+        const int s = c % STAGES;
+        ok = mbar_wait(smem_u32(&bar_full[s]), (c / STAGES) & 1u);
         if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
+        const int count = min(CHUNK, nblk - c * CHUNK);
+        for (int j = 0; j < count; ++j) {
+          const uint64_t adesc = make_desc(sbase + (uint32_t)j * SLAB_BYTES, 2048u, 1024u, 2u);
+          const uint64_t bdesc = make_desc(sbase + STAGE_SLABS + (uint32_t)j * BLOCK_BYTES, 16u, 256u, 6u);
+          const uint32_t accumulate = (c > 0 || j > 0) ? 1u : 0u;
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t"
+              "setp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem),
+              "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+              : "memory");
+        }
+        const uint32_t arrive_on = (c == nchunks - 1) ? smem_u32(&bar_done) : smem_u32(&bar_empty[s]);
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(arrive_on)
+                     : "memory");
       }
-      issue_loads(c + 1, s ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
-    // The copies were made through the generic proxy; the MMA reads through the async proxy.
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
-      const int count = min(CHUNK, nblk - c * CHUNK);
-      for (int j = 0; j < count; ++j) {
-        const uint32_t item = sbase + (uint32_t)j * ITEM_BYTES;
-        const uint64_t adesc = make_desc(item, 2048u, 128u);
-        const uint64_t bdesc = make_desc(item + SLAB_BYTES, 256u, 128u);
-        const uint32_t accumulate = (c > 0 || j > 0) ? 1u : 0u;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
-            : "memory");
-      }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                       smem_u32(&mbar[s]))
-                   : "memory");
+    if (!ok) {
+      failed = 1;
+      atomicExch(status, 1);
+      // Release the waiters below.
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_done)) : "memory");
     }
   }
-  if (ok) {  // the last chunk's MMAs
-    const int s = (nchunks - 1) & 1;
-    ok = mbar_wait(smem_u32(&mbar[s]), uses[s] & 1u);
-  }
-  ok = __syncthreads_and(ok);
-  if (!ok) {
-    failed = 1;
-    atomicExch(status, 1);
-  }
-  asm volatile("cp.async.wait_all;" ::: "memory");
+  // The four epilogue warps wait for the last MMA (or for the failure release).
+  bool done_ok = warp < 4 ? mbar_wait(smem_u32(&bar_done), 0u) : true;
+  done_ok = __syncthreads_and(done_ok);
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  __syncthreads();
+  if (!done_ok && tid == 0) atomicExch(status, 1);
 
-  if (!failed) {
+  if (done_ok && !failed && warp < 4) {
     uint32_t v[16];
     const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
     asm volatile(
@@ -225,7 +223,7 @@ __global__ void __launch_bounds__(128) bsr16_spmm_tcgen05_kernel(
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    const int64_t col = n0 + warp * 32 + lane;  // TMEM lane m = column n0 + m of C
+    const int64_t col = (int64_t)n0 + warp * 32 + lane;  // TMEM lane m = column n0 + m of C
     if (col < N) {
 #pragma unroll
       for (int r = 0; r < 16; ++r) C[(br * 16 + r) * N + col] = __float2bfloat16_rn(__uint_as_float(v[r]));
@@ -237,11 +235,42 @@ __global__ void __launch_bounds__(128) bsr16_spmm_tcgen05_kernel(
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows.
+bool make_map_2d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                 uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * 2};  // bytes between rows
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 bool bsr16_tcgen05_supported(const BsrSpmmArgs &a) {
-  return a.block_size == 16 && a.n_rhs % 8 == 0 && (reinterpret_cast<uintptr_t>(a.B) & 15u) == 0 &&
-         (reinterpret_cast<uintptr_t>(a.block_values) & 15u) == 0;
+  // TMA needs 16-byte aligned bases and row pitches.
+  return a.block_size == 16 && a.n_rhs % 8 == 0 && a.nnzb > 0 && a.cols > 0 &&
+         (reinterpret_cast<uintptr_t>(a.B) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.block_values) & 15u) == 0;
 }
 
 cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, const DeviceInfo &dev,
@@ -261,9 +290,16 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, co
   const int64_t n_tiles = ceil_div(a.n_rhs, TILE_N);
   const int64_t grid = brows * n_tiles;
   if (grid > 2147483647LL) return cudaErrorInvalidConfiguration;
-  bsr16_spmm_tcgen05_kernel<<<(unsigned)grid, 128, SMEM_BYTES, s>>>(
-      n_tiles, a.n_rhs, a.block_row_ptr, a.block_col_idx, static_cast<const __nv_bfloat16 *>(a.block_values),
-      static_cast<const __nv_bfloat16 *>(a.B), static_cast<__nv_bfloat16 *>(a.C), status_flag);
+  CUtensorMap map_B, map_A;
+  // B: cols x N bf16, boxes of 64 columns x 16 rows, 128-byte swizzle.
+  if (!make_map_2d(&map_B, a.B, (uint64_t)a.n_rhs, (uint64_t)a.cols, 64, 16, CU_TENSOR_MAP_SWIZZLE_128B))
+    return cudaErrorInvalidValue;
+  // Block values as (nnzb*16) x 16 bf16, one 16 x 16 box per block, 32-byte swizzle.
+  if (!make_map_2d(&map_A, a.block_values, 16, (uint64_t)a.nnzb * 16, 16, 16, CU_TENSOR_MAP_SWIZZLE_32B))
+    return cudaErrorInvalidValue;
+  bsr16_spmm_tcgen05_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(
+      map_B, map_A, n_tiles, a.n_rhs, a.block_row_ptr, a.block_col_idx, static_cast<__nv_bfloat16 *>(a.C),
+      status_flag);
   ++*launches;
   return cudaGetLastError();
 }
