@@ -110,7 +110,8 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
-                "samples": len(self.samples)}
+                "samples": len(self.samples),
+                "window": "warm-up, timed steps and up to 1 s more of the same steps"}
 
 
 def build_workload(name: str, device, rows):
@@ -260,14 +261,22 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    launches0 = ctx.kernel_launches
+    # Clocks are sampled from the warm-up on; because one nvidia-smi query takes longer than a short
+    # timed region, the same steps keep running (untimed) afterwards until a few samples exist.
     with ClockSampler(local) as clocks:
-        total_ms = timed(step, args.steps)
+        for _ in range(max(args.warmup, 3)):
+            step()
         barrier()
-    gpu_launches = ctx.kernel_launches - launches0
+        launches0 = ctx.kernel_launches
+        total_ms = timed(step, args.steps)
+        launches1 = ctx.kernel_launches
+        barrier()
+        t_soak = time.perf_counter()
+        while len(clocks.samples) < 4 and time.perf_counter() - t_soak < 1.0:
+            for _ in range(10):
+                step()
+            torch.cuda.synchronize()
+    gpu_launches = launches1 - launches0
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     gbs = wl["bytes"] / (ms_per_step * 1e-3) / 1e9

@@ -65,6 +65,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
     """Compiles and links the library; returns its path."""
     OBJDIR.mkdir(parents=True, exist_ok=True)
     extra = ["-Xptxas", "-v"] if ptxas_info else []
+    extra += os.environ.get("SWB_EXTRA_NVCC_FLAGS", "").split()
     srcs = sources()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose, extra), srcs))

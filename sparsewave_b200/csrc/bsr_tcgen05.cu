@@ -44,8 +44,14 @@ namespace swb {
 namespace {
 
 constexpr int TILE_N = 128;                  // right-hand-side columns per CTA (MMA M)
-constexpr int CHUNK = 4;                     // blocks per pipeline stage
-constexpr int STAGES = 4;
+#ifndef SWB_BSR_CHUNK
+#define SWB_BSR_CHUNK 2
+#endif
+#ifndef SWB_BSR_STAGES
+#define SWB_BSR_STAGES 2
+#endif
+constexpr int CHUNK = SWB_BSR_CHUNK;         // blocks per pipeline stage
+constexpr int STAGES = SWB_BSR_STAGES;
 constexpr int SLAB_BYTES = 16 * TILE_N * 2;  // 4096: one 16 x 128 bf16 slab
 constexpr int HALF_SLAB = SLAB_BYTES / 2;    // 2048: 64 columns x 16 rows
 constexpr int BLOCK_BYTES = 16 * 16 * 2;     // 512
