@@ -111,7 +111,7 @@ class ClockSampler:
         reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
                 "samples": len(self.samples),
-                "window": "warm-up, timed steps and up to 1 s more of the same steps"}
+                "window": "warm-up, timed steps and about 0.3 s more of the same steps"}
 
 
 def build_workload(name: str, device, rows):
@@ -271,11 +271,13 @@ def run_ours(args):
         total_ms = timed(step, args.steps)
         launches1 = ctx.kernel_launches
         barrier()
-        t_soak = time.perf_counter()
-        while len(clocks.samples) < 4 and time.perf_counter() - t_soak < 1.0:
-            for _ in range(10):
-                step()
-            torch.cuda.synchronize()
+        # Keep the same steps running for about 0.3 s so that the sampler sees the clocks under this
+        # load.  The step count comes from the rank-reduced time, so every rank runs the same number
+        # of steps (they contain a collective when N > 1).
+        soak_steps = int(min(5000, max(10, 300.0 / max(max_over_ranks(total_ms) / args.steps, 1e-3))))
+        for _ in range(soak_steps):
+            step()
+        barrier()
     gpu_launches = launches1 - launches0
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps

@@ -1,0 +1,58 @@
+"""Row-sharded SpMV / SpMM over two GPUs with the NCCL all-gather (skipped with fewer than two GPUs)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port):
+    import torch.distributed as dist
+
+    import oracle
+    from sparsewave_b200 import Context, sharding, workloads as W
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = Context(rank)
+        a, x = W.config_c3(device="cuda", rows=1 << 16, max_len=4096)
+        B = W.dense_uniform((a.cols, 8), seed=9, device="cuda")
+        shard = sharding.shard_csr(a.row_ptr, a.col_idx, a.values, a.cols, rank, world)
+        lo, hi = sharding.owned_dense_range(a.cols, world, rank)
+        rp, ci, v = a.numpy()
+        xh, Bh = x.cpu().numpy(), B.cpu().numpy()
+        rows = slice(shard.row_begin, shard.row_end)
+        op = sharding.ShardedOperator(ctx, shard, "spmv-mapping=wave-per-position")
+        y = op.spmv(x[lo:hi].contiguous()).cpu().numpy()
+        bound = oracle.csr_abs_bound(rp, ci, v, xh)[rows]
+        assert np.all(np.abs(y - oracle.csr_spmv(rp, ci, v, xh)[rows]) <= 1e-5 * bound + 1e-30)
+        op = sharding.ShardedOperator(ctx, shard, "spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128")
+        C = op.spmm(B[lo:hi].contiguous()).cpu().numpy()
+        bound = oracle.csr_abs_bound(rp, ci, v, Bh)[rows]
+        assert np.all(np.abs(C - oracle.csr_spmm(rp, ci, v, Bh)[rows]) <= 1e-5 * bound + 1e-30)
+        # shard boundaries are the same on every rank
+        b = torch.tensor(sharding.shard_boundaries(a.row_ptr, world), device="cuda")
+        ref = b.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(b, ref)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sharded_operators():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_rank_main, args=(2, _free_port()), nprocs=2, join=True)
