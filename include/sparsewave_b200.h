@@ -184,6 +184,38 @@ SWB_API int swb_bsr_spmm_bf16(swb_context *ctx, const swb_options *opts,
                               const uint16_t *block_values, const uint16_t *B,
                               uint16_t *C, swb_stream stream);
 
+/* The tensor-core BSR SpMM (16x16 bf16 blocks, f32 accumulation, bf16 output)
+ * for callers that must not allocate device memory.  It has no counterpart in
+ * the reference; it exists because the entry point above needs a context, and
+ * creating a context allocates the status word the kernel raises when one of
+ * its bounded barrier waits gives up.  A caller that lives under a memory
+ * budget fixed at start-up, that is loaded into a process which forbids
+ * allocations after initialisation, or that may run while the allocator is
+ * locked cannot do that.  This entry point takes no context, calls no
+ * cudaMalloc / cudaFree and keeps its status words in a fixed 128 KiB array
+ * inside the library image (held by every GPU that loads the library until
+ * the process exits), one word per (block row, 128-column tile) pair.
+ *   - Limit: (rows / 16) * ceil(n_rhs / 128) <= 32768, else SWB_ERR_CAPACITY.
+ *   - Needs nnzb > 0, n_rhs % 8 == 0 and 16-byte aligned block_values and B,
+ *     else SWB_ERR_UNSUPPORTED (there is no second kernel behind it).
+ *   - The first call on a device looks up the array's device address; make
+ *     that call before any stream capture begins.
+ *   - Every call shares the array and first clears the words it uses, so it
+ *     holds the outcome of the latest call only, and calls that overlap on
+ *     the GPU race on it.
+ *   - gave_up_ctas: NULL for an asynchronous call; otherwise the call
+ *     synchronises `stream` and stores how many CTAs abandoned a wait (0 = the
+ *     output is valid).
+ * Errors are reported through swb_last_error(NULL). */
+SWB_API int swb_bsr16_spmm_bf16_static(int64_t rows, int64_t cols, int64_t nnzb,
+                                       int64_t n_rhs,
+                                       const int32_t *block_row_ptr,
+                                       const int32_t *block_col_idx,
+                                       const uint16_t *block_values,
+                                       const uint16_t *B, uint16_t *C,
+                                       swb_stream stream,
+                                       int32_t *gave_up_ctas);
+
 /* ---- operators, host buffers ------------------------------------------- */
 /* Same contracts with HOST pointers: the call copies the operands to the
  * context's device workspace (grown on demand and kept), runs the kernel,

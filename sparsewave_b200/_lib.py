@@ -79,6 +79,7 @@ SIGNATURES = {
     "swb_spmm": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_f32": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_bf16": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
+    "swb_bsr16_spmm_bf16_static": (C.c_int, [_I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(C.c_int32)]),
     "swb_spmv_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "swb_spmm_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_bf16_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P]),

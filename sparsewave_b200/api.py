@@ -240,6 +240,27 @@ class Context:
                                                  _host_ptr(col_idx, torch.int32, "col_idx")))
 
 
+def bsr16_spmm_bf16_static(block_row_ptr, block_col_idx, block_values, B, C_out=None, *, wait: bool = True):
+    """16x16 bf16 BSR SpMM through the entry point that allocates no device memory
+    (no context; status words in the library's fixed array).  With `wait` the call
+    synchronises the current stream and raises if any CTA abandoned a wait."""
+    lib = _lib.load()
+    rows, cols, n_rhs = int(block_row_ptr.numel() - 1) * 16, int(B.shape[0]), int(B.shape[1])
+    if C_out is None:
+        C_out = torch.empty((rows, n_rhs), dtype=torch.bfloat16, device=B.device)
+    gave_up = C.c_int32(-1)
+    st = lib.swb_bsr16_spmm_bf16_static(
+        rows, cols, int(block_col_idx.numel()), n_rhs, _dev_ptr(block_row_ptr, torch.int32, "block_row_ptr"),
+        _dev_ptr(block_col_idx, torch.int32, "block_col_idx"), _dev_ptr(block_values, torch.bfloat16, "block_values"),
+        _dev_ptr(B, torch.bfloat16, "B"), _dev_ptr(C_out, torch.bfloat16, "C"),
+        torch.cuda.current_stream(B.device).cuda_stream, C.byref(gave_up) if wait else None)
+    if st != 0:
+        raise SparseWaveError(st, lib.swb_last_error(None).decode())
+    if wait and gave_up.value != 0:
+        raise SparseWaveError(_lib.SWB_ERR_CUDA, f"{gave_up.value} CTAs abandoned a barrier wait")
+    return C_out
+
+
 # -- context-free helpers (host arithmetic only; need no GPU) ---------------------------
 
 def partition(lower: int, upper: int, worker: int, count: int) -> tuple[int, int]:

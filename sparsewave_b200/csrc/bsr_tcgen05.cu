@@ -37,6 +37,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdio>
+
 #include "swb_index.h"
 #include "swb_kernels.h"
 
@@ -104,6 +106,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+// PER_CTA_STATUS: raise status[blockIdx.x] instead of status[0] when a wait gives up.
+template <bool PER_CTA_STATUS>
 __global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_B, const __grid_constant__ CUtensorMap map_A, int64_t n_tiles,
     int64_t N, const int32_t *__restrict__ brp, const int32_t *__restrict__ bci, __nv_bfloat16 *__restrict__ C,
@@ -207,7 +211,7 @@ __global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
     }
     if (!ok) {
       failed = 1;
-      atomicExch(status, 1);
+      atomicExch(status + (PER_CTA_STATUS ? blockIdx.x : 0), 1);
       // Release the waiters below.
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_done)) : "memory");
     }
@@ -216,7 +220,7 @@ __global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
   bool done_ok = warp < 4 ? mbar_wait(smem_u32(&bar_done), 0u) : true;
   done_ok = __syncthreads_and(done_ok);
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (!done_ok && tid == 0) atomicExch(status, 1);
+  if (!done_ok && tid == 0) atomicExch(status + (PER_CTA_STATUS ? blockIdx.x : 0), 1);
 
   if (done_ok && !failed && warp < 4) {
     uint32_t v[16];
@@ -286,7 +290,7 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, co
   int device = 0;
   cudaGetDevice(&device);
   if (device < 0 || device >= 64 || !configured[device]) {
-    cudaError_t e = cudaFuncSetAttribute(bsr16_spmm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(bsr16_spmm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_BYTES);
     if (e != cudaSuccess) return e;
     if (device >= 0 && device < 64) configured[device] = true;
@@ -303,7 +307,7 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, co
   // Block values as (nnzb*16) x 16 bf16, one 16 x 16 box per block, 32-byte swizzle.
   if (!make_map_2d(&map_A, a.block_values, 16, (uint64_t)a.nnzb * 16, 16, 16, CU_TENSOR_MAP_SWIZZLE_32B))
     return cudaErrorInvalidValue;
-  bsr16_spmm_tcgen05_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(
+  bsr16_spmm_tcgen05_kernel<false><<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(
       map_B, map_A, n_tiles, a.n_rhs, a.block_row_ptr, a.block_col_idx, static_cast<__nv_bfloat16 *>(a.C),
       status_flag);
   ++*launches;
@@ -311,3 +315,127 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, co
 }
 
 }  // namespace swb
+
+// ---------------------------------------------------------------------------
+// swb_bsr16_spmm_bf16_static: the tensor-core BSR SpMM for callers that must
+// not allocate device memory.
+//
+// The regular entry point needs a context, and creating a context calls
+// cudaMalloc for the status word its kernels raise when a bounded barrier wait
+// gives up.  Some callers cannot do that: code running under a memory budget
+// that was fixed at start-up (every byte handed out by the application's own
+// pool), plug-ins that are loaded into a process which forbids driver
+// allocations after initialisation, and code that runs while the allocator's
+// lock may be held.  For them the status words live in the fixed array below,
+// which is part of the library image: every GPU that loads the library holds
+// its 128 KiB until the process exits, whether or not this entry point is used.
+//
+// One status word per CTA (block row x tile of 128 columns), hence the limit
+// of SWB_STATIC_MAX_CTAS CTAs per call.  All calls share the array and a call
+// begins by clearing the words it will use, so the array holds the outcome of
+// the most recent call only, and two calls that overlap on the GPU (different
+// streams) race on it.
+// ---------------------------------------------------------------------------
+namespace swb {
+namespace {
+
+constexpr int SWB_STATIC_MAX_CTAS = 32768;  // 32768 status words = 128 KiB
+
+static __device__ __align__(256) int swb_static_status_words[SWB_STATIC_MAX_CTAS];
+
+// In host code `swb_static_status_words` is only a handle for the symbol, not a
+// device address; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int *static_status_address(cudaError_t *err) {
+  static int *address[64] = {};
+  int device = 0;
+  *err = cudaGetDevice(&device);
+  if (*err != cudaSuccess) return nullptr;
+  if (device < 0 || device >= 64) {
+    *err = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  if (!address[device]) {
+    void *p = nullptr;
+    *err = cudaGetSymbolAddress(&p, swb_static_status_words);
+    if (*err != cudaSuccess) return nullptr;
+    address[device] = static_cast<int *>(p);
+  }
+  return address[device];
+}
+
+int static_fail(int status, const char *fmt, long long a = 0, long long b = 0) {
+  char buf[512];
+  snprintf(buf, sizeof buf, fmt, a, b);
+  set_thread_error(buf);
+  return status;
+}
+
+}  // namespace
+}  // namespace swb
+
+extern "C" __attribute__((visibility("default"))) int swb_bsr16_spmm_bf16_static(
+    int64_t rows, int64_t cols, int64_t nnzb, int64_t n_rhs, const int32_t *block_row_ptr,
+    const int32_t *block_col_idx, const uint16_t *block_values, const uint16_t *B, uint16_t *C, void *stream,
+    int32_t *gave_up_ctas) {
+  using namespace swb;
+  // Status codes are those of swb_status in sparsewave_b200.h.
+  constexpr int kInvalidShape = -2, kInvalidArgument = -3, kCuda = -4, kUnsupported = -5, kCapacity = -7;
+  if (rows < 0 || cols < 0 || nnzb < 0)
+    return static_fail(kInvalidArgument, "bsr_spmm: rows, cols and nnzb must be non-negative");
+  if (rows % 16 != 0)
+    return static_fail(kInvalidShape, "output rows must be divisible by block size, but got %lld and 16", rows);
+  if (cols % 16 != 0)
+    return static_fail(kInvalidShape, "right-hand-side rows must be divisible by block size, but got %lld and 16", cols);
+  if (n_rhs < 1) return static_fail(kInvalidShape, "bsr_spmm: right-hand side must have at least one column, but got %lld", n_rhs);
+  if (rows > 2147483647LL || cols > 2147483647LL || nnzb > 2147483647LL / 16)
+    return static_fail(kInvalidShape, "BSR dimensions and NNZ blocks must fit in i32");
+  if (!block_row_ptr || (nnzb > 0 && (!block_col_idx || !block_values)) || (cols > 0 && !B) || (rows > 0 && !C))
+    return static_fail(kInvalidArgument, "bsr_spmm: NULL operand pointer");
+  BsrSpmmArgs a{rows, cols, nnzb, 16, n_rhs, block_row_ptr, block_col_idx, block_values, B, C};
+  if (!bsr16_tcgen05_supported(a))
+    return static_fail(kUnsupported,
+                       "the static-scratch BSR entry point needs at least one block, a column count that is a "
+                       "multiple of 8 and 16-byte aligned block values and right-hand side");
+  const int64_t n_tiles = ceil_div(n_rhs, TILE_N);
+  const int64_t grid = (rows / 16) * n_tiles;
+  if (grid > SWB_STATIC_MAX_CTAS)
+    return static_fail(kCapacity,
+                       "the static-scratch BSR entry point handles at most %lld (block row, 128-column tile) pairs "
+                       "per call, but this call needs %lld",
+                       (long long)SWB_STATIC_MAX_CTAS, (long long)grid);
+  if (grid == 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+  int *status = static_status_address(&e);
+  if (!status) return static_fail(kCuda, cudaGetErrorString(e));
+  e = cudaFuncSetAttribute(bsr16_spmm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
+  CUtensorMap map_B, map_A;
+  if (!make_map_2d(&map_B, B, (uint64_t)n_rhs, (uint64_t)cols, 64, 16, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_map_2d(&map_A, block_values, 16, (uint64_t)nnzb * 16, 16, 16, CU_TENSOR_MAP_SWIZZLE_32B))
+    return static_fail(kCuda, "could not encode the TMA tensor maps");
+  // The words keep the previous call's outcome: clear the ones this call uses.
+  e = cudaMemsetAsync(status, 0, (size_t)grid * sizeof(int), s);
+  if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
+  bsr16_spmm_tcgen05_kernel<true><<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(
+      map_B, map_A, n_tiles, n_rhs, block_row_ptr, block_col_idx, reinterpret_cast<__nv_bfloat16 *>(C), status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
+  if (gave_up_ctas) {
+    // Host copy of the status words through pageable memory on the stack, in
+    // pieces: no pinned or device allocation.
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
+    int32_t count = 0;
+    int piece[1024];
+    for (int64_t off = 0; off < grid; off += 1024) {
+      const int64_t n = grid - off < 1024 ? grid - off : 1024;
+      e = cudaMemcpy(piece, status + off, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost);
+      if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
+      for (int64_t i = 0; i < n; ++i) count += piece[i] != 0;
+    }
+    *gave_up_ctas = count;
+  }
+  return 0;
+}

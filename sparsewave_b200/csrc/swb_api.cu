@@ -44,6 +44,14 @@ int fail(swb_context *ctx, int status, const char *fmt, ...) {
   return status;
 }
 
+}  // namespace
+
+namespace swb {
+void set_thread_error(const char *message) { g_thread_error = message ? message : ""; }
+}  // namespace swb
+
+namespace {
+
 int cuda_fail(swb_context *ctx, cudaError_t e, const char *what) {
   return fail(ctx, SWB_ERR_CUDA, "CUDA error in %s: %s", what, cudaGetErrorString(e));
 }

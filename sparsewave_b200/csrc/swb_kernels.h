@@ -99,4 +99,7 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag,
                                       const DeviceInfo &dev, cudaStream_t s,
                                       int64_t *launches);
 
+// Stores the diagnostic that swb_last_error(NULL) returns on this thread.
+void set_thread_error(const char *message);
+
 }  // namespace swb
