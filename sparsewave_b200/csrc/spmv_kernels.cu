@@ -23,6 +23,14 @@ __device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
 __device__ __forceinline__ int4 ld_stream(const int4 *p) { return __ldcs(p); }
 __device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
 
+// Gather of one x element: read-only path, no L1 allocation (the 13 % L1 hit
+// rate of a random gather does not pay for the fills).
+__device__ __forceinline__ float ld_x(const float *p) {
+  float v;
+  asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 // XOR butterfly, offsets 1,2,4,8,16: every lane ends with the warp sum
 // (buildWaveReduction, SparseGPUUtils.cpp:236-245).
 __device__ __forceinline__ float warp_sum(float v) {

@@ -110,10 +110,10 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
     load_chunk(cb + SPAN_CHUNK, cn, vn);
     const bool m0 = p0 + 0 >= sb && p0 + 0 < ce, m1 = p0 + 1 >= sb && p0 + 1 < ce;
     const bool m2 = p0 + 2 >= sb && p0 + 2 < ce, m3 = p0 + 3 >= sb && p0 + 3 < ce;
-    const float q0 = m0 ? mul(v.x, __ldg(x + c.x)) : 0.0f;
-    const float q1 = m1 ? mul(v.y, __ldg(x + c.y)) : 0.0f;
-    const float q2 = m2 ? mul(v.z, __ldg(x + c.z)) : 0.0f;
-    const float q3 = m3 ? mul(v.w, __ldg(x + c.w)) : 0.0f;
+    const float q0 = m0 ? mul(v.x, ld_x(x + c.x)) : 0.0f;
+    const float q1 = m1 ? mul(v.y, ld_x(x + c.y)) : 0.0f;
+    const float q2 = m2 ? mul(v.z, ld_x(x + c.z)) : 0.0f;
+    const float q3 = m3 ? mul(v.w, ld_x(x + c.w)) : 0.0f;
 
     if (next_b >= ce) {
       // The whole chunk lies in row R.
