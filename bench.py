@@ -46,8 +46,9 @@ WORKLOADS = {
                name="c5: BSR SpMM 16384x16384, 16x16 bf16 blocks at 5% density, N=512"),
 }
 
-# DRAM bytes per launch of the dominant kernel from ncu captures (profiles/), or None.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the full workload size,
+# from the one-pass ncu captures summarised under profiles/ (None where no capture exists).
+NCU_TRAFFIC_BYTES = {"c3": 1.095e9, "c4": 16.71e9, "c5": 45.3e6}
 
 
 def parse_args():
