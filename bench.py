@@ -62,6 +62,9 @@ def parse_args():
     p.add_argument("--rows", type=int, default=None, help="override the row count (testing)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu", action="store_true")
+    p.add_argument("--compare-library", action="store_true",
+                   help="also time cuSPARSE (through torch.sparse) on the same operands, like the reference's "
+                        "rocSPARSE column; comparison only")
     p.add_argument("--replicated", action="store_true",
                    help="N > 1: dense operand already replicated, no all-gather in the step")
     return p.parse_args()
@@ -285,6 +288,19 @@ def run_ours(args):
     gbs = wl["bytes"] / (ms_per_step * 1e-3) / 1e9
     gflops = wl["flops"] / (ms_per_step * 1e-3) / 1e9
 
+    # ---- vendor library on the same operands (comparison column only) ---------------------------
+    library = None
+    if args.compare_library and world == 1 and kind in ("spmv", "spmm"):
+        A = torch.sparse_csr_tensor(a.row_ptr, a.col_idx, a.values, size=(a.rows, a.cols))
+        lib_step = (lambda: torch.mv(A, dense)) if kind == "spmv" else (lambda: torch.mm(A, dense))
+        for _ in range(3):
+            lib_step()
+        torch.cuda.synchronize()
+        lib_ms = timed(lib_step, args.steps) / args.steps
+        library = {"name": "cuSPARSE via torch.sparse_csr", "ms_per_step": lib_ms,
+                   "value": wl["bytes"] / (lib_ms * 1e-3) / 1e9, "unit": "GB/s"}
+        del A
+
     # ---- end to end through the host-buffer C-ABI call --------------------------------------
     e2e = None
     if not args.no_e2e:
@@ -322,6 +338,8 @@ def run_ours(args):
             line["roofline"]["tensor"] = {"achieved_tflops": gflops / 1e3, "peak_tflops": tf_peak,
                                           "frac": gflops / 1e3 / tf_peak}
         line["cpu_baseline"] = cpu
+        if library is not None:
+            line["library_baseline"] = library
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
