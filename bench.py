@@ -60,6 +60,8 @@ def parse_args():
     p.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     p.add_argument("--options", default=None, help="option string in the reference's spelling")
     p.add_argument("--rows", type=int, default=None, help="override the row count (testing)")
+    p.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying "
+                   "a CUDA graph of one step")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu", action="store_true")
     p.add_argument("--compare-library", action="store_true",
@@ -196,6 +198,8 @@ def run_ours(args):
     ctx = Context(local)
     spec = WORKLOADS[args.workload]
     options = args.options if args.options is not None else spec["options"]
+    from sparsewave_b200 import make_options
+    opts = make_options(options)  # parsed once; the steps pass the option block
     wl = build_workload(args.workload, device, args.rows)
     kind, a, dense = wl["kind"], wl["a"], wl["dense"]
     if kind == "bsr" and world > 1:
@@ -204,7 +208,7 @@ def run_ours(args):
     # ---- this rank's share --------------------------------------------------------------
     if world > 1:
         shard = sharding.shard_csr(a.row_ptr, a.col_idx, a.values, a.cols, rank, world)
-        op = sharding.ShardedOperator(ctx, shard, options)
+        op = sharding.ShardedOperator(ctx, shard, opts)
         lo, hi = sharding.owned_dense_range(a.cols, world, rank)
         owned = dense[lo:hi].contiguous()
         out = torch.empty((shard.rows,) + tuple(dense.shape[1:]), dtype=torch.float32, device=device)
@@ -217,13 +221,13 @@ def run_ours(args):
     else:
         if kind == "spmv":
             out = torch.empty(a.rows, dtype=torch.float32, device=device)
-            step = lambda: ctx.spmv(options, a.row_ptr, a.col_idx, a.values, dense, out)
+            step = lambda: ctx.spmv(opts, a.row_ptr, a.col_idx, a.values, dense, out)
         elif kind == "spmm":
             out = torch.empty((a.rows, dense.shape[1]), dtype=torch.float32, device=device)
-            step = lambda: ctx.spmm(options, a.row_ptr, a.col_idx, a.values, dense, out)
+            step = lambda: ctx.spmm(opts, a.row_ptr, a.col_idx, a.values, dense, out)
         else:
             out = torch.empty((a.rows, dense.shape[1]), dtype=torch.bfloat16, device=device)
-            step = lambda: ctx.bsr_spmm(options, a.block_row_ptr, a.block_col_idx, a.block_values, dense, 16, out)
+            step = lambda: ctx.bsr_spmm(opts, a.block_row_ptr, a.block_col_idx, a.block_values, dense, 16, out)
         local_input_bytes = wl["bytes"]
 
     def barrier():
@@ -271,6 +275,25 @@ def run_ours(args):
         for _ in range(max(args.warmup, 3)):
             step()
         barrier()
+        # One step (collective + kernels) captured in a CUDA graph and replayed: the timed loop then has no
+        # per-step host work.  Workloads that need the L2 flush between steps stay on host launches, and so
+        # do steps that contain the NCCL all-gather (capturing the collective hung here, so it is not tried).
+        eager_step, launches_per_step, graph = step, None, None
+        has_collective = world > 1 and not args.replicated
+        if flush is None and not args.no_graph and not has_collective:
+            try:
+                before = ctx.kernel_launches
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    eager_step()
+                launches_per_step = ctx.kernel_launches - before
+                g.replay()
+                torch.cuda.synchronize()
+                graph, step = g, g.replay
+            except Exception as exc:  # noqa: BLE001
+                print(f"bench: CUDA graph capture failed, launching from the host: {exc}", file=sys.stderr)
+                torch.cuda.synchronize()
+        barrier()
         launches0 = ctx.kernel_launches
         total_ms = timed(step, args.steps)
         launches1 = ctx.kernel_launches
@@ -282,7 +305,7 @@ def run_ours(args):
         for _ in range(soak_steps):
             step()
         barrier()
-    gpu_launches = launches1 - launches0
+    gpu_launches = launches1 - launches0 if graph is None else launches_per_step * args.steps
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     gbs = wl["bytes"] / (ms_per_step * 1e-3) / 1e9
@@ -326,7 +349,8 @@ def run_ours(args):
         "config": {"workload": spec["name"], "options": options, **describe(wl),
                    "bytes_algorithmic": wl["bytes"], "flops": wl["flops"],
                    "dense_operand": "replicated" if (world == 1 or args.replicated) else "all-gathered each step",
-                   "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps"},
+                   "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
+                   "launch": "CUDA graph of one step, replayed" if graph is not None else "host launch per step"},
         "gflops": gflops, "frac_of_hbm_peak": gbs / (peak * world), "gpu_launches": int(gpu_launches),
         "clocks": clocks.summary(), "e2e": e2e,
     }
