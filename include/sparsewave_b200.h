@@ -152,6 +152,15 @@ SWB_API int swb_spmv(swb_context *ctx, const swb_options *opts, int64_t rows,
                      const int32_t *col_idx, const float *val, const float *x,
                      float *y, swb_stream stream);
 
+/* sparsewave.coo_spmv (SparseWaveOps.td, COOSpMVOp; lowering
+ * ThreadPerNonzeroCOOSpMVPattern, SparseWaveToGPU.cpp:154-214): y is zero
+ * filled, then every entry adds val[p] * x[col_idx[p]] to y[row_idx[p]];
+ * duplicate coordinates accumulate.  Uses opts->block_size. */
+SWB_API int swb_coo_spmv(swb_context *ctx, const swb_options *opts, int64_t rows,
+                         int64_t cols, int64_t nnz, const int32_t *row_idx,
+                         const int32_t *col_idx, const float *val,
+                         const float *x, float *y, swb_stream stream);
+
 /* sparsewave.spmm (SparseWaveOps.td:91-124): C[r, j] = sum_p val[p] *
  * B[col[p], j].  B is cols x n_rhs and C is rows x n_rhs, both row-major with
  * identity layout (SparseBenchmarkUtils.cpp:261-268). */

@@ -68,6 +68,13 @@ def csr_spmv(row_ptr, col, val, x, parallel: bool = False) -> np.ndarray:
     return y
 
 
+def coo_spmv(rows, row, col, val, x) -> np.ndarray:
+    row, col, val, x = _i32(row), _i32(col), _f32(val), _f32(x)
+    y = np.empty(rows, dtype=np.float32)
+    lib().oracle_coo_spmv(_I64(rows), _I64(len(val)), _ptr(row), _ptr(col), _ptr(val), _ptr(x), _ptr(y))
+    return y
+
+
 def csr_spmm(row_ptr, col, val, B, parallel: bool = False) -> np.ndarray:
     row_ptr, col, val, B = _i32(row_ptr), _i32(col), _f32(val), _f32(B)
     rows, n = len(row_ptr) - 1, B.shape[1]

@@ -12,7 +12,7 @@
  * test/TorchExport/csr_spmm_hip_runtime.mlir:12), the folded index answers of
  * position-space-lowering.mlir:200-222,226-243,343-356, and agree with the
  * reference's own CPU loops compiled from benchmark/SparseBenchmarkUtils.cpp
- * (oracle/build_ref.py) on that file's fixed inputs.
+ * (oracle/build.py) on that file's fixed inputs.
  *
  * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (oracle/build.py).
  * -ffp-contract=off keeps every product and sum a separate f32 operation,
@@ -358,6 +358,15 @@ ORACLE_API void oracle_spmm_thread_position(
       C[row * n + j] += val[p] * B[(int64_t)col[p] * n + j];
     }
   }
+}
+
+/* COO SpMV: benchmark/SparseBenchmarkUtils.cpp:243-256 (expected output of
+ * loadCOOSpMVBenchmarkInputs) and ThreadPerNonzeroCOOSpMVPattern
+ * (SparseWaveToGPU.cpp:154-214): zero fill, then entries in storage order. */
+ORACLE_API void oracle_coo_spmv(int64_t rows, int64_t nnz, const int32_t *row, const int32_t *col,
+                                const float *val, const float *x, float *y) {
+  for (int64_t r = 0; r < rows; ++r) y[r] = 0.0f;
+  for (int64_t p = 0; p < nnz; ++p) y[row[p]] += val[p] * x[col[p]];
 }
 
 /* ---- mismatch counters ------------------------------------------------------ */

@@ -76,6 +76,7 @@ SIGNATURES = {
     "swb_options_parse": (C.c_int, [_CTX, _OPT, C.c_char_p]),
     "swb_options_validate": (C.c_int, [_CTX, _OPT]),
     "swb_spmv": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
+    "swb_coo_spmv": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_spmm": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_f32": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_bf16": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),

@@ -147,6 +147,18 @@ class Context:
             _dev_ptr(y, torch.float32, "y"), self._stream()))
         return y
 
+    def coo_spmv(self, options, rows: int, row_idx, col_idx, val, x, y=None):
+        """y = A @ x for COO A (entries in any order, duplicates accumulate)."""
+        cols, nnz = int(x.numel()), int(val.numel())
+        if y is None:
+            y = torch.empty(rows, dtype=torch.float32, device=x.device)
+        o = self._opts(options)
+        self._check(self._lib.swb_coo_spmv(
+            self._ctx, C.byref(o), int(rows), cols, nnz, _dev_ptr(row_idx, torch.int32, "row_idx"),
+            _dev_ptr(col_idx, torch.int32, "col_idx"), _dev_ptr(val, torch.float32, "val"),
+            _dev_ptr(x, torch.float32, "x"), _dev_ptr(y, torch.float32, "y"), self._stream()))
+        return y
+
     def spmv_position_trace(self, options, row_ptr, col_idx, val, x):
         """Position-mapped SpMV that also returns (row, worker, segment_end) per position."""
         rows, cols, nnz = int(row_ptr.numel() - 1), int(x.numel()), int(val.numel())

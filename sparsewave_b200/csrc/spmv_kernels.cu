@@ -238,6 +238,21 @@ __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64
 }
 
 // ---------------------------------------------------------------------------
+// COO SpMV, thread-per-nonzero (ThreadPerNonzeroCOOSpMVPattern,
+// SparseWaveToGPU.cpp:154-214): zero fill, then position = blockIdx * blockDim
+// + threadIdx adds val * x[col] to y[row] with one atomicAdd; duplicate
+// coordinates simply add twice.
+// ---------------------------------------------------------------------------
+__global__ void coo_spmv_thread_per_nonzero_kernel(int64_t nnz, const int32_t *__restrict__ row,
+                                                   const int32_t *__restrict__ col,
+                                                   const float *__restrict__ val,
+                                                   const float *__restrict__ x, float *__restrict__ y) {
+  const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= nnz) return;
+  atomicAdd(y + ld_stream(row + p), mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))));
+}
+
+// ---------------------------------------------------------------------------
 // wave-per-position (WavePositionReducePattern, SparsePositionScheduling.cpp:
 // 318-403; segmented scan buildWavePrefixSegmentedReduction,
 // SparseGPUUtils.cpp:247-292).
@@ -474,6 +489,16 @@ cudaError_t launch_fill_zero(float *y, int64_t n, int block, cudaStream_t s, int
   int64_t blocks = max1(ceil_div(n, block));
   if (blocks > 148 * 32) blocks = 148 * 32;
   fill_zero_kernel<<<(unsigned)blocks, block, 0, s>>>(y, n);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_coo_spmv_thread_per_nonzero(int64_t rows, int64_t nnz, const int32_t *row, const int32_t *col,
+                                               const float *val, const float *x, float *y, int block,
+                                               cudaStream_t s, int64_t *launches) {
+  cudaError_t e = launch_fill_zero(y, rows, block, s, launches);
+  if (e != cudaSuccess) return e;
+  coo_spmv_thread_per_nonzero_kernel<<<grid_of(ceil_div(nnz, block)), block, 0, s>>>(nnz, row, col, val, x, y);
   ++*launches;
   return cudaGetLastError();
 }

@@ -502,6 +502,27 @@ int swb_spmv(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
                    static_cast<cudaStream_t>(stream));
 }
 
+int swb_coo_spmv(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
+                 const int32_t *row_idx, const int32_t *col_idx, const float *val, const float *x, float *y,
+                 swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  st = swb_options_validate(ctx, o);
+  if (st != SWB_OK) return st;
+  if (rows < 0 || cols < 0 || nnz < 0)
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "coo_spmv: rows, cols and nnz must be non-negative");
+  // i32 coordinates (benchmark/benchmark_utils.py:214-223)
+  if (rows > kI32Max || cols > kI32Max || nnz > kI32Max)
+    return fail(ctx, SWB_ERR_INVALID_SHAPE, "coo_spmv: matrix dimensions and NNZ must fit in the i32 COO type");
+  if ((nnz > 0 && (!row_idx || !col_idx || !val)) || (cols > 0 && !x) || (rows > 0 && !y))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "coo_spmv: NULL operand pointer");
+  cudaError_t e = swb::launch_coo_spmv_thread_per_nonzero(rows, nnz, row_idx, col_idx, val, x, y,
+                                                          (int)o->block_size, static_cast<cudaStream_t>(stream),
+                                                          &ctx->launches);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "coo_spmv launch");
+  return SWB_OK;
+}
+
 int swb_spmv_position_trace(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
                             const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x,
                             float *y, int32_t *row_of_position, int32_t *worker_of_position,

@@ -52,6 +52,11 @@ struct DeviceInfo {
 cudaError_t launch_fill_zero(float *y, int64_t n, int block, cudaStream_t s,
                              int64_t *launches);
 
+// --- COO SpMV (zero fill + one atomic per nonzero)
+cudaError_t launch_coo_spmv_thread_per_nonzero(int64_t rows, int64_t nnz, const int32_t *row, const int32_t *col,
+                                               const float *val, const float *x, float *y, int block,
+                                               cudaStream_t s, int64_t *launches);
+
 // --- SpMV row mappings
 cudaError_t launch_spmv_thread_per_row(const CsrSpmvArgs &a, int block,
                                        cudaStream_t s, int64_t *launches);

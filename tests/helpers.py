@@ -21,6 +21,10 @@ SPMM_GOLDEN_TORCH = dict(row_ptr=[0, 2, 3], col=[0, 2, 1], val=[1, 2, 3],
 BSR_GOLDEN = dict(brp=[0, 2, 3], bci=[0, 1, 0], bv=[1, 2, 0, 3, 4, 0, 5, 6, 7, 0, 0, 8], bs=2,
                   B=[[1, 10], [2, 20], [3, 30], [4, 40]], C=[[17, 170], [45, 450], [7, 70], [16, 160]])
 
+# test/Dialect/SparseWave/coo-spmv-runtime.mlir:22-40 (duplicate coordinate (0, 0))
+COO_GOLDEN = dict(rows=4, row=[0, 0, 0, 1, 2, 2, 3], col=[0, 0, 2, 1, 0, 3, 2], val=[0.25, 0.75, 2, 3, 4, 5, 6],
+                  x=[10, 20, 30, 40], y=[70, 60, 240, 180])
+
 SPMV_MAPPING_OPTIONS = [
     "spmv-mapping=thread-per-row",
     "spmv-mapping=wave-per-row",

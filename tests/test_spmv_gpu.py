@@ -5,7 +5,7 @@ import torch
 
 import oracle
 from sparsewave_b200 import workloads as W
-from tests.helpers import (SPMV_GOLDEN, SPMV_GOLDEN_4X4, SPMV_MAPPING_OPTIONS, assert_within_bound, dev, random_csr)
+from tests.helpers import (COO_GOLDEN, SPMV_GOLDEN, SPMV_GOLDEN_4X4, SPMV_MAPPING_OPTIONS, assert_within_bound, dev, random_csr)
 
 pytestmark = pytest.mark.gpu
 
@@ -150,3 +150,22 @@ def test_full_size_power_law_properties(ctx):
     # checksum against the host: sum_r y[r] == sum_p val[p] * x[col[p]] in f64
     total = (a.values.double() * x[a.col_idx.long()].double()).sum()
     assert abs(float(y1.double().sum() - total)) <= 1e-6 * float(babs.double().sum())
+
+
+@pytest.mark.parametrize("block", [32, 128, 1024])
+def test_coo_spmv(ctx, block):
+    g = COO_GOLDEN
+    y = ctx.coo_spmv(f"block-size={block}", g["rows"], dev(g["row"], torch.int32), dev(g["col"], torch.int32),
+                     dev(g["val"], torch.float32), dev(g["x"], torch.float32))
+    assert y.cpu().tolist() == g["y"]
+    # unordered entries with duplicates against the oracle's sequential accumulation
+    rng = np.random.default_rng(block)
+    rows, cols, nnz = 700, 500, 20000
+    ri, ci = rng.integers(0, rows, nnz).astype(np.int32), rng.integers(0, cols, nnz).astype(np.int32)
+    v, x = rng.uniform(-1, 1, nnz).astype(np.float32), rng.uniform(-1, 1, cols).astype(np.float32)
+    y = ctx.coo_spmv(f"block-size={block}", rows, dev(ri), dev(ci), dev(v), dev(x)).cpu().numpy()
+    bound = np.zeros(rows)
+    np.add.at(bound, ri, np.abs(v.astype(np.float64) * x[ci]))
+    assert_within_bound(y, oracle.coo_spmv(rows, ri, ci, v, x), bound)
+    assert ctx.coo_spmv("", 3, dev(np.zeros(0, np.int32)), dev(np.zeros(0, np.int32)), dev(np.zeros(0, np.float32)),
+                        dev(x)).cpu().tolist() == [0, 0, 0]
