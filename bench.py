@@ -67,6 +67,8 @@ def parse_args():
     p.add_argument("--compare-library", action="store_true",
                    help="also time cuSPARSE (through torch.sparse) on the same operands, like the reference's "
                         "rocSPARSE column; comparison only")
+    p.add_argument("--torch-collective", action="store_true",
+                   help="N > 1: all-gather through torch.distributed instead of the library's communicator")
     p.add_argument("--replicated", action="store_true",
                    help="N > 1: dense operand already replicated, no all-gather in the step")
     return p.parse_args()
@@ -196,6 +198,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     ctx = Context(local)
+    if world > 1 and not args.torch_collective:
+        ctx.comm_init(rank, world)  # the library's own NCCL communicator (capturable in the step's CUDA graph)
     spec = WORKLOADS[args.workload]
     options = args.options if args.options is not None else spec["options"]
     from sparsewave_b200 import make_options
@@ -231,6 +235,9 @@ def run_ours(args):
         local_input_bytes = wl["bytes"]
 
     def barrier():
+        # Drain this rank's queue first: the library's communicator and torch.distributed's are two NCCL
+        # communicators on the same GPUs, and collectives of both in flight at once can wait on each other.
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -277,19 +284,22 @@ def run_ours(args):
         barrier()
         # One step (collective + kernels) captured in a CUDA graph and replayed: the timed loop then has no
         # per-step host work.  Workloads that need the L2 flush between steps stay on host launches, and so
-        # do steps that contain the NCCL all-gather (capturing the collective hung here, so it is not tried).
+        # do steps whose all-gather goes through torch.distributed (capturing that one hung here, so it is not
+        # tried); the library's own ncclAllGather is captured with the kernels.
         eager_step, launches_per_step, graph = step, None, None
-        has_collective = world > 1 and not args.replicated
-        if flush is None and not args.no_graph and not has_collective:
+        torch_collective = world > 1 and not args.replicated and args.torch_collective
+        if flush is None and not args.no_graph and not torch_collective:
             try:
                 before = ctx.kernel_launches
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                # relaxed: NCCL's helper threads may issue CUDA calls of their own while this thread captures
+                with torch.cuda.graph(g, capture_error_mode="relaxed"):
                     eager_step()
                 launches_per_step = ctx.kernel_launches - before
                 g.replay()
                 torch.cuda.synchronize()
                 graph, step = g, g.replay
+                g = None
             except Exception as exc:  # noqa: BLE001
                 print(f"bench: CUDA graph capture failed, launching from the host: {exc}", file=sys.stderr)
                 torch.cuda.synchronize()
@@ -339,7 +349,19 @@ def run_ours(args):
                "ms_per_pass": best * 1e3,
                "sample": f"{passes} passes over the whole workload, best pass, OpenMP over rows"}
 
+    def shutdown():
+        # Orderly on every rank: drop the graph (it holds the captured collective), drain the GPU, release
+        # the library's communicator, then torch.distributed's.
+        nonlocal graph, step
+        graph = step = None
+        torch.cuda.synchronize()
+        ctx.close()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
     if rank != 0:
+        shutdown()
         return
     peak, tf_peak, peak_kind = measured_peaks()
     line = {
@@ -348,7 +370,9 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16" if kind == "bsr" else "f32", "data": "synthetic",
         "config": {"workload": spec["name"], "options": options, **describe(wl),
                    "bytes_algorithmic": wl["bytes"], "flops": wl["flops"],
-                   "dense_operand": "replicated" if (world == 1 or args.replicated) else "all-gathered each step",
+                   "dense_operand": "replicated" if (world == 1 or args.replicated) else
+                   ("all-gathered each step (torch.distributed)" if args.torch_collective
+                    else "all-gathered each step (library NCCL communicator)"),
                    "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
                    "launch": "CUDA graph of one step, replayed" if graph is not None else "host launch per step"},
         "gflops": gflops, "frac_of_hbm_peak": gbs / (peak * world), "gpu_launches": int(gpu_launches),
@@ -365,8 +389,7 @@ def run_ours(args):
         if library is not None:
             line["library_baseline"] = library
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown()
 
 
 def run_e2e(args, ctx, wl, options, rank, world, device, barrier, max_over_ranks):

@@ -362,6 +362,22 @@ SWB_API int swb_spmv_position_trace(swb_context *ctx, const swb_options *opts,
                                     int32_t *worker_of_position,
                                     int32_t *segment_end, swb_stream stream);
 
+/* ---- multi-GPU communicator ------------------------------------------------ */
+/* One NCCL communicator per context over the GPUs of one node (one process per
+ * GPU).  Not a reference feature.  Rank 0 makes the 128-byte id with
+ * swb_comm_unique_id and hands it to the other ranks by any host channel;
+ * every rank then calls swb_comm_init (collective: it returns once all ranks
+ * have joined).  swb_comm_allgather gathers `bytes_per_rank` bytes from every
+ * rank into `recv` (rank k's bytes at offset k * bytes_per_rank) on `stream`:
+ * the exchange of the dense operand (x or B) that precedes the local kernel
+ * of a row shard.  swb_destroy releases the communicator. */
+SWB_API int swb_comm_unique_id(uint8_t id[128]);
+SWB_API int swb_comm_init(swb_context *ctx, const uint8_t id[128], int n_ranks,
+                          int rank);
+SWB_API int swb_comm_allgather(swb_context *ctx, const void *send, void *recv,
+                               int64_t bytes_per_rank, swb_stream stream);
+SWB_API void swb_comm_destroy(swb_context *ctx);
+
 /* ---- multi-GPU row sharding --------------------------------------------- */
 /* nnz-balanced contiguous row shards: boundaries[k] = the first row r with
  * row_ptr[r] >= k * nnz / n_shards (exact integer arithmetic), boundaries[0]

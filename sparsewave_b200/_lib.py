@@ -97,6 +97,10 @@ SIGNATURES = {
     "swb_row_at_position": (_I64, [_P, _I64, _I64]),
     "swb_launch_shape_query": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, C.POINTER(SwbLaunchShape)]),
     "swb_spmv_position_trace": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "swb_comm_unique_id": (C.c_int, [_P]),
+    "swb_comm_init": (C.c_int, [_CTX, _P, C.c_int, C.c_int]),
+    "swb_comm_allgather": (C.c_int, [_CTX, _P, _P, _I64, _P]),
+    "swb_comm_destroy": (None, [_CTX]),
     "swb_shard_rows_by_nnz": (C.c_int, [_CTX, _P, _I64, _I64, _P]),
 }
 

@@ -123,6 +123,37 @@ class Context:
         self._check(self._lib.swb_device_status(self._ctx, self._stream(), C.byref(v)))
         return int(v.value)
 
+    # -- multi-GPU communicator (NCCL, bound inside the library) ---------------------
+    def comm_init(self, rank: int, world: int, group=None) -> None:
+        """Creates this context's NCCL communicator.  Collective over `group` (a torch.distributed
+        group, used only to hand rank 0's unique id to the other ranks)."""
+        import torch.distributed as dist
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            st = self._lib.swb_comm_unique_id(buf)
+            if st != 0:
+                raise SparseWaveError(st, self._lib.swb_last_error(None).decode())
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        if world > 1:
+            backend = dist.get_backend(group)
+            t = ident.cuda(self.device) if backend == "nccl" else ident
+            dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            ident = t.cpu()
+        raw = (C.c_uint8 * 128)(*ident.tolist())
+        self._check(self._lib.swb_comm_init(self._ctx, raw, int(world), int(rank)))
+        self.comm_world, self.comm_rank = int(world), int(rank)
+
+    def allgather(self, send: torch.Tensor, recv: torch.Tensor) -> torch.Tensor:
+        """recv[k * n : (k + 1) * n] = rank k's `send` (n elements), on the current stream."""
+        if not (send.is_cuda and recv.is_cuda and send.is_contiguous() and recv.is_contiguous()):
+            raise TypeError("allgather needs contiguous CUDA tensors")
+        nbytes = send.numel() * send.element_size()
+        if recv.numel() * recv.element_size() != nbytes * getattr(self, "comm_world", 1):
+            raise ValueError("recv must hold world x send bytes")
+        self._check(self._lib.swb_comm_allgather(self._ctx, send.data_ptr(), recv.data_ptr(), nbytes, self._stream()))
+        return recv
+
     def validate(self, options) -> None:
         self._check(self._lib.swb_options_validate(self._ctx, C.byref(self._opts(options))))
 

@@ -25,6 +25,8 @@ struct swb_context {
   size_t workspace_used = 0;
   cudaStream_t host_stream = nullptr;
   int *status_flag = nullptr;  // device int for kernels with bounded waits
+  void *comm = nullptr;        // NCCL communicator of the multi-GPU path (swb_comm.cu)
+  int comm_ranks = 1, comm_rank = 0;
 };
 
 namespace {
@@ -48,6 +50,16 @@ int fail(swb_context *ctx, int status, const char *fmt, ...) {
 
 namespace swb {
 void set_thread_error(const char *message) { g_thread_error = message ? message : ""; }
+void set_context_error(swb_context *ctx, const char *message) {
+  if (ctx) ctx->error = message ? message : ""; else set_thread_error(message);
+}
+int context_device(const swb_context *ctx) { return ctx->device; }
+void *context_comm(const swb_context *ctx) { return ctx->comm; }
+void set_context_comm(swb_context *ctx, void *comm, int n_ranks, int rank) {
+  ctx->comm = comm;
+  ctx->comm_ranks = n_ranks;
+  ctx->comm_rank = rank;
+}
 }  // namespace swb
 
 namespace {
@@ -194,6 +206,7 @@ int swb_device_status(swb_context *ctx, swb_stream stream, int32_t *status) {
 void swb_destroy(swb_context *ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
+  swb_comm_destroy(ctx);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->status_flag) cudaFree(ctx->status_flag);
   if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);

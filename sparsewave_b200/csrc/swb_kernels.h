@@ -104,6 +104,15 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag,
                                       const DeviceInfo &dev, cudaStream_t s,
                                       int64_t *launches);
 
+// Context accessors for translation units that do not see the context's layout.
+}  // namespace swb
+struct swb_context;
+namespace swb {
+void set_context_error(swb_context *ctx, const char *message);
+int context_device(const swb_context *ctx);
+void *context_comm(const swb_context *ctx);
+void set_context_comm(swb_context *ctx, void *comm, int n_ranks, int rank);
+
 // Stores the diagnostic that swb_last_error(NULL) returns on this thread.
 void set_thread_error(const char *message);
 

@@ -76,10 +76,14 @@ def shard_csr(row_ptr: torch.Tensor, col_idx: torch.Tensor, values: torch.Tensor
                     values[p0:p1].contiguous())
 
 
-def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
+def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor] = None, group=None,
+                    ctx: Optional[api.Context] = None) -> torch.Tensor:
     """Gathers every rank's chunk of the dense operand (leading dimension split
-    by `dense_chunk`) into a full copy on this rank; returns its first n_rows rows."""
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    by `dense_chunk`) into a full copy on this rank; returns its first n_rows rows.
+    With a context that owns a communicator (`Context.comm_init`) the exchange is the
+    library's own NCCL all-gather on the current stream; otherwise torch.distributed's."""
+    native = ctx is not None and getattr(ctx, "comm_world", 0) > 1
+    world = ctx.comm_world if native else (dist.get_world_size(group) if dist.is_initialized() else 1)
     chunk = dense_chunk(n_rows, world)
     tail = tuple(owned.shape[1:])
     if out is None:
@@ -91,7 +95,10 @@ def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor
     if owned.shape[0] != chunk:  # the last rank's chunk may be short: pad to the common size
         send = torch.zeros((chunk,) + tail, dtype=owned.dtype, device=owned.device)
         send[:owned.shape[0]].copy_(owned)
-    dist.all_gather_into_tensor(out.view(-1), send.contiguous().view(-1), group=group)
+    if native:
+        ctx.allgather(send.contiguous().view(-1), out.view(-1))
+    else:
+        dist.all_gather_into_tensor(out.view(-1), send.contiguous().view(-1), group=group)
     return out[:n_rows]
 
 
@@ -109,7 +116,7 @@ class ShardedOperator:
         shape = (chunk * world,) + tuple(owned.shape[1:])
         if self._full is None or tuple(self._full.shape) != shape or self._full.dtype != owned.dtype:
             self._full = torch.empty(shape, dtype=owned.dtype, device=owned.device)
-        return allgather_dense(owned, n_rows, self._full, self.group)
+        return allgather_dense(owned, n_rows, self._full, self.group, self.ctx)
 
     def spmv(self, x_owned: torch.Tensor, y_local: Optional[torch.Tensor] = None, *, replicated_x=None):
         """y[row_begin:row_end] = A_shard @ x.  `x_owned` is this rank's chunk of x;

@@ -34,7 +34,10 @@ def _rank_main(rank, world, port):
         xh, Bh = x.cpu().numpy(), B.cpu().numpy()
         rows = slice(shard.row_begin, shard.row_end)
         op = sharding.ShardedOperator(ctx, shard, "spmv-mapping=wave-per-position")
-        y = op.spmv(x[lo:hi].contiguous()).cpu().numpy()
+        y = op.spmv(x[lo:hi].contiguous()).cpu().numpy()   # all-gather through torch.distributed
+        ctx.comm_init(rank, world)                          # from here on: the library's own communicator
+        y2 = op.spmv(x[lo:hi].contiguous()).cpu().numpy()
+        assert np.all(np.abs(y2 - y) <= 1e-5 * oracle.csr_abs_bound(rp, ci, v, xh)[rows] + 1e-30)
         bound = oracle.csr_abs_bound(rp, ci, v, xh)[rows]
         assert np.all(np.abs(y - oracle.csr_spmv(rp, ci, v, xh)[rows]) <= 1e-5 * bound + 1e-30)
         op = sharding.ShardedOperator(ctx, shard, "spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128")
