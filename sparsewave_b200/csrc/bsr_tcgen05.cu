@@ -279,6 +279,8 @@ bool make_map_2d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t ou
 
 bool bsr16_tcgen05_supported(const BsrSpmmArgs &a) {
   // TMA needs 16-byte aligned bases and row pitches.
+  // ... and 32-bit box coordinates: block rows of the value matrix (nnzb * 16) and B's extents.
+  if (a.nnzb > 2147483647LL / 16 || a.cols > 2147483647LL || a.n_rhs > 2147483647LL - 256) return false;
   return a.block_size == 16 && a.n_rhs % 8 == 0 && a.nnzb > 0 && a.cols > 0 &&
          (reinterpret_cast<uintptr_t>(a.B) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.block_values) & 15u) == 0;
 }

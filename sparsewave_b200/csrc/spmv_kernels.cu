@@ -192,7 +192,66 @@ __global__ void spmv_block_per_row_kernel(int64_t rows, const int32_t *__restric
 // per-position search would.  atomic: one atomicAdd per position.  segmented:
 // one atomicAdd per row change plus one at the chunk end.
 // ---------------------------------------------------------------------------
-template <bool SEGMENTED, bool TRACE>
+__device__ __forceinline__ int warp_row_search(const int32_t *__restrict__ row_ptr, int len, int pos, int lane);
+
+// Row of the first position of every worker of a block, found by the block
+// together instead of one 22-step binary search per thread: warp 0 searches
+// the row of the block's first position (32-ary, five dependent loads for 4 M
+// rows); the block then streams the row offsets that follow with coalesced
+// loads, each offset b inside the block's position range [cb, ce) marks the
+// first worker that starts at or after b (atomicMax keeps the last of several
+// rows that start at one position, i.e. skips empty rows), and a block-wide
+// prefix maximum gives every worker the last row that starts at or before its
+// first position - the value of the reference's upper-bound search
+// (SparsePositionToSCF.cpp:225-271).  Needs blockDim.x to be a multiple of 32.
+__device__ __forceinline__ int block_first_rows(const int32_t *__restrict__ row_ptr, int64_t rows, int64_t cb,
+                                                int64_t ce, int64_t chunk, int *marks, int *warp_tot) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  __shared__ int first_row;
+  if (warp == 0) {
+    const int r = warp_row_search(row_ptr, (int)rows + 1, (int)cb, lane);
+    if (lane == 0) first_row = r;
+  }
+  marks[tid] = -1;
+  __syncthreads();
+  const int R0 = first_row;
+  if (tid == 0) marks[0] = R0;
+  __syncthreads();
+  for (int64_t r0 = (int64_t)R0 + 1;; r0 += blockDim.x) {
+    const int64_t r = r0 + tid;
+    int64_t b = INT64_MAX;
+    if (r <= rows) b = __ldg(row_ptr + r);
+    const bool inside = b < ce;
+    if (inside) {
+      const int64_t w = (b - cb + chunk - 1) / chunk;  // first worker whose chunk starts at or after b
+      if (w < blockDim.x) atomicMax(&marks[w], (int)r);
+    }
+    if (!__syncthreads_and(inside)) break;
+  }
+  // inclusive prefix maximum over the block
+  int v = marks[tid];
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int t = __shfl_up_sync(FULL, v, off);
+    if (lane >= off) v = max(v, t);
+  }
+  if (lane == 31) warp_tot[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int t = lane < nwarps ? warp_tot[lane] : -1;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int u = __shfl_up_sync(FULL, t, off);
+      if (lane >= off) t = max(t, u);
+    }
+    warp_tot[lane] = t;  // inclusive over warps
+  }
+  __syncthreads();
+  if (warp > 0) v = max(v, warp_tot[warp - 1]);
+  return v;
+}
+
+template <bool SEGMENTED, bool TRACE, bool COOP>
 __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64_t chunk,
                                                 const int32_t *__restrict__ row_ptr,
                                                 const int32_t *__restrict__ col,
@@ -202,8 +261,24 @@ __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64
   const int64_t worker = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t begin, end;
   chunk_bounds(0, nnz, worker, chunk, begin, end);
-  if (begin >= end) return;
-  int64_t row = row_at_position(row_ptr, rows + 1, begin);
+  int64_t row;
+  if (COOP) {
+    __shared__ int marks[1024];
+    __shared__ int warp_tot[32];
+    // positions of this block: workers blockIdx*B .. +B, clipped to nnz (uniform for the block)
+    const int64_t w0 = (int64_t)blockIdx.x * blockDim.x;
+    int64_t cb, ce, unused;
+    chunk_bounds(0, nnz, w0, chunk, cb, unused);
+    const int64_t last = w0 + blockDim.x - 1;
+    chunk_bounds(0, nnz, last, chunk, unused, ce);
+    if (ce <= cb) ce = nnz;  // the last worker of the block is past the end: the block reaches nnz
+    if (w0 * chunk >= nnz) return;  // whole block inactive (only the clamped grid of an empty matrix)
+    row = block_first_rows(row_ptr, rows, cb, ce, chunk, marks, warp_tot);
+    if (begin >= end) return;
+  } else {
+    if (begin >= end) return;
+    row = row_at_position(row_ptr, rows + 1, begin);
+  }
   int64_t next = row_ptr[row + 1];
   float acc = 0.0f;
   int64_t acc_row = row;
@@ -536,21 +611,23 @@ cudaError_t launch_spmv_thread_per_position(const CsrSpmvArgs &a, int block, int
   if (e != cudaSuccess) return e;
   const int64_t workers = ceil_div(a.nnz, chunk);
   const unsigned grid = grid_of(ceil_div(workers, block));
+  // Blocks made of whole warps recover rows cooperatively; other block sizes search per thread.
+  const bool coop = block % 32 == 0;
+#define SWB_TPP(SEG, TR)                                                                         \
+  do {                                                                                           \
+    if (coop)                                                                                    \
+      spmv_thread_per_position_kernel<SEG, TR, true><<<grid, block, 0, s>>>(                      \
+          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);                    \
+    else                                                                                         \
+      spmv_thread_per_position_kernel<SEG, TR, false><<<grid, block, 0, s>>>(                     \
+          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);                    \
+  } while (0)
   if (trace.enabled()) {
-    if (segmented)
-      spmv_thread_per_position_kernel<true, true><<<grid, block, 0, s>>>(
-          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
-    else
-      spmv_thread_per_position_kernel<false, true><<<grid, block, 0, s>>>(
-          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+    if (segmented) SWB_TPP(true, true); else SWB_TPP(false, true);
   } else {
-    if (segmented)
-      spmv_thread_per_position_kernel<true, false><<<grid, block, 0, s>>>(
-          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
-    else
-      spmv_thread_per_position_kernel<false, false><<<grid, block, 0, s>>>(
-          a.rows, a.nnz, chunk, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);
+    if (segmented) SWB_TPP(true, false); else SWB_TPP(false, false);
   }
+#undef SWB_TPP
   ++*launches;
   return cudaGetLastError();
 }

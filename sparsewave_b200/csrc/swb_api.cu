@@ -485,6 +485,10 @@ static int spmv_impl(swb_context *ctx, const swb_options *o, int64_t rows, int64
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL operand pointer");
   if (trace.enabled() && !is_position_mapping(o->mapping))
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "position trace requires a position mapping");
+  // The position kernels step through positions in 32-bit chunks of up to 4096 past the end.
+  if (is_position_mapping(o->mapping) && nnz > kI32Max - 65536)
+    return fail(ctx, SWB_ERR_UNSUPPORTED, "position mappings support at most %lld nonzeros, but got %lld",
+                (long long)(kI32Max - 65536), (long long)nnz);
   swb::CsrSpmvArgs a{rows, cols, nnz, row_ptr, col_idx, val, x, y};
   const int B = (int)o->block_size;
   cudaError_t e = cudaSuccess;
