@@ -67,6 +67,8 @@ def parse_args():
     p.add_argument("--compare-library", action="store_true",
                    help="also time cuSPARSE (through torch.sparse) on the same operands, like the reference's "
                         "rocSPARSE column; comparison only")
+    p.add_argument("--overlap", action="store_true",
+                   help="N > 1: run the locally-owned columns of the shard while the all-gather is in flight")
     p.add_argument("--torch-collective", action="store_true",
                    help="N > 1: all-gather through torch.distributed instead of the library's communicator")
     p.add_argument("--replicated", action="store_true",
@@ -212,12 +214,16 @@ def run_ours(args):
     # ---- this rank's share --------------------------------------------------------------
     if world > 1:
         shard = sharding.shard_csr(a.row_ptr, a.col_idx, a.values, a.cols, rank, world)
-        op = sharding.ShardedOperator(ctx, shard, opts)
+        overlap = args.overlap and not args.replicated and not args.torch_collective
+        op = sharding.OverlappedShardedOperator(ctx, shard, opts) if overlap else \
+            sharding.ShardedOperator(ctx, shard, opts)
         lo, hi = sharding.owned_dense_range(a.cols, world, rank)
         owned = dense[lo:hi].contiguous()
         out = torch.empty((shard.rows,) + tuple(dense.shape[1:]), dtype=torch.float32, device=device)
         full = dense if args.replicated else None
-        if kind == "spmv":
+        if overlap:
+            step = (lambda: op.spmv(owned, out)) if kind == "spmv" else (lambda: op.spmm(owned, out))
+        elif kind == "spmv":
             step = lambda: op.spmv(owned, out, replicated_x=full)
         else:
             step = lambda: op.spmm(owned, out, replicated_B=full)
@@ -372,7 +378,8 @@ def run_ours(args):
                    "bytes_algorithmic": wl["bytes"], "flops": wl["flops"],
                    "dense_operand": "replicated" if (world == 1 or args.replicated) else
                    ("all-gathered each step (torch.distributed)" if args.torch_collective
-                    else "all-gathered each step (library NCCL communicator)"),
+                    else "all-gathered each step (library NCCL communicator)" +
+                    (", overlapped with the locally-owned columns" if args.overlap else "")),
                    "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
                    "launch": "CUDA graph of one step, replayed" if graph is not None else "host launch per step"},
         "gflops": gflops, "frac_of_hbm_peak": gbs / (peak * world), "gpu_launches": int(gpu_launches),

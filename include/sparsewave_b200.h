@@ -88,7 +88,12 @@ typedef struct swb_options {
   int32_t mapping;                  /* swb_spmv_mapping, default thread-per-row  */
   int32_t position_reduction;       /* swb_position_reduction, default atomic    */
   int32_t spmm_mapping;             /* swb_spmm_mapping, default thread-per-output */
-  int32_t reserved0;
+  /* Not a reference option.  0 (default): the output is overwritten, as every
+   * reference lowering does.  1: the result is added to the existing output
+   * (position mappings skip their zero fill; wave-per-row-tile adds on store).
+   * Used by the multi-GPU layer to run the locally-owned columns of a row
+   * shard while the all-gather of the remote part of x / B is in flight. */
+  int32_t accumulate;
   int64_t block_size;               /* SpMV threads per block, default 256       */
   int64_t wave_size;                /* default 32                                */
   int64_t position_block_size;      /* position-parallel block size, default 256 */

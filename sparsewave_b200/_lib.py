@@ -26,7 +26,7 @@ class SwbOptions(C.Structure):
         ("mapping", C.c_int32),
         ("position_reduction", C.c_int32),
         ("spmm_mapping", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("accumulate", C.c_int32),
         ("block_size", C.c_int64),
         ("wave_size", C.c_int64),
         ("position_block_size", C.c_int64),

@@ -120,7 +120,8 @@ __global__ void spmm_wave_per_row_tile_kernel(int64_t rows, int64_t N, int T, in
                                               const int32_t *__restrict__ row_ptr,
                                               const int32_t *__restrict__ col,
                                               const float *__restrict__ val,
-                                              const float *__restrict__ B, float *__restrict__ C) {
+                                              const float *__restrict__ B, float *__restrict__ C,
+                                              bool accumulate) {
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= rows * tiles) return;
@@ -155,7 +156,10 @@ __global__ void spmm_wave_per_row_tile_kernel(int64_t rows, int64_t N, int T, in
 
   tile_reduce<TCAP>(acc, lane);
   const int k = tile_column_of_lane<TCAP>(lane);
-  if (lane_is_column_writer<TCAP>(lane) && k < T && j0 + k < N) C[row * N + j0 + k] = acc[0];
+  if (lane_is_column_writer<TCAP>(lane) && k < T && j0 + k < N) {
+    float *out = C + row * N + j0 + k;
+    *out = accumulate ? add(*out, acc[0]) : acc[0];
+  }
 }
 
 // Full tiles of 4, 8, 16 or 32 columns with 16-byte aligned B and C rows.  The
@@ -171,7 +175,8 @@ __global__ void spmm_wave_per_row_tile_vec_kernel(int64_t rows, int64_t N, int64
                                                   const int32_t *__restrict__ row_ptr,
                                                   const int32_t *__restrict__ col,
                                                   const float *__restrict__ val,
-                                                  const float *__restrict__ B, float *__restrict__ C) {
+                                                  const float *__restrict__ B, float *__restrict__ C,
+                                                  bool accumulate) {
   constexpr int T = 4 * G, PG = 32 / G;
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -216,7 +221,10 @@ __global__ void spmm_wave_per_row_tile_vec_kernel(int64_t rows, int64_t N, int64
 #pragma unroll
   for (int off = 4; off >= G; off >>= 1) r = add(r, __shfl_xor_sync(FULL, r, off));
   const int comp = (up16 ? 2 : 0) + (up8 ? 1 : 0);
-  if ((lane & 7 & ~(G - 1)) == 0) C[row * N + j0 + 4 * cq + comp] = r;
+  if ((lane & 7 & ~(G - 1)) == 0) {
+    float *out = C + row * N + j0 + 4 * cq + comp;
+    *out = accumulate ? add(*out, r) : r;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -270,10 +278,10 @@ cudaError_t launch_tile(const CsrSpmmArgs &a, int block, int T, cudaStream_t s) 
   if (vec) {
     if constexpr (TCAP >= 4)
       spmm_wave_per_row_tile_vec_kernel<TCAP / 4><<<grid, block, 0, s>>>(a.rows, a.n_rhs, tiles, a.row_ptr,
-                                                                          a.col_idx, a.val, a.B, a.C);
+                                                                          a.col_idx, a.val, a.B, a.C, a.accumulate);
   } else {
     spmm_wave_per_row_tile_kernel<TCAP><<<grid, block, 0, s>>>(
-        a.rows, a.n_rhs, T, tiles, a.row_ptr, a.col_idx, a.val, a.B, a.C);
+        a.rows, a.n_rhs, T, tiles, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
   }
   return cudaGetLastError();
 }
@@ -303,8 +311,10 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
 cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block, int64_t chunk,
                                             cudaStream_t s, int64_t *launches) {
   // Zero fill of the flattened output, then the atomic schedule.
-  cudaError_t e = launch_fill_zero(a.C, a.rows * a.n_rhs, block, s, launches);
-  if (e != cudaSuccess) return e;
+  if (!a.accumulate) {
+    cudaError_t e = launch_fill_zero(a.C, a.rows * a.n_rhs, block, s, launches);
+    if (e != cudaSuccess) return e;
+  }
   const int64_t workers = ceil_div(a.nnz * a.n_rhs, chunk);
   const unsigned grid = (unsigned)max1(ceil_div(workers, block));
   spmm_thread_per_position_kernel<<<grid, block, 0, s>>>(a.rows, a.nnz, a.n_rhs, chunk, a.row_ptr,

@@ -607,8 +607,10 @@ cudaError_t launch_spmv_block_per_row(const CsrSpmvArgs &a, int block, cudaStrea
 cudaError_t launch_spmv_thread_per_position(const CsrSpmvArgs &a, int block, int64_t chunk,
                                             bool segmented, const PositionTrace &trace,
                                             cudaStream_t s, int64_t *launches) {
-  cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
-  if (e != cudaSuccess) return e;
+  if (!a.accumulate) {
+    cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
+    if (e != cudaSuccess) return e;
+  }
   const int64_t workers = ceil_div(a.nnz, chunk);
   const unsigned grid = grid_of(ceil_div(workers, block));
   // Blocks made of whole warps recover rows cooperatively; other block sizes search per thread.
@@ -652,8 +654,10 @@ int64_t wave_per_position_physical_grid(int64_t nnz, int block, int64_t batch) {
 cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64_t batch,
                                           const PositionTrace &trace, cudaStream_t s,
                                           int64_t *launches, int64_t *physical_grid) {
-  cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
-  if (e != cudaSuccess) return e;
+  if (!a.accumulate) {
+    cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
+    if (e != cudaSuccess) return e;
+  }
   const int64_t waves = wave_position_wave_count(a.nnz, block);
   const int64_t grid = wave_per_position_physical_grid(a.nnz, block, batch);
   if (physical_grid) *physical_grid = grid;

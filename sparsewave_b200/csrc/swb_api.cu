@@ -296,6 +296,11 @@ int swb_options_parse(swb_context *ctx, swb_options *o, const char *text) {
     else if (key == "spmm-tile-size") st = want_int(o->spmm_tile_size);
     else if (key == "spmm-position-chunk-size") st = want_int(o->spmm_position_chunk_size);
     else if (key == "wave-position-batch") st = want_int(o->wave_position_batch);
+    else if (key == "accumulate") {
+      int64_t v = 0;
+      st = want_int(v);
+      o->accumulate = v != 0;
+    }
     else {
       bool foreign = false;
       for (const ForeignBlockSize &f : kForeign) {
@@ -489,7 +494,10 @@ static int spmv_impl(swb_context *ctx, const swb_options *o, int64_t rows, int64
   if (is_position_mapping(o->mapping) && nnz > kI32Max - 65536)
     return fail(ctx, SWB_ERR_UNSUPPORTED, "position mappings support at most %lld nonzeros, but got %lld",
                 (long long)(kI32Max - 65536), (long long)nnz);
+  if (o->accumulate && !is_position_mapping(o->mapping))
+    return fail(ctx, SWB_ERR_UNSUPPORTED, "accumulate is available for the position mappings of SpMV only");
   swb::CsrSpmvArgs a{rows, cols, nnz, row_ptr, col_idx, val, x, y};
+  a.accumulate = o->accumulate != 0;
   const int B = (int)o->block_size;
   cudaError_t e = cudaSuccess;
   switch (o->mapping) {
@@ -573,7 +581,10 @@ int swb_spmm(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
   if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
   if (!row_ptr || (nnz > 0 && (!col_idx || !val)) || (cols > 0 && !B) || (rows > 0 && !C))
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL operand pointer");
+  if (o->accumulate && o->spmm_mapping == SWB_THREAD_PER_OUTPUT)
+    return fail(ctx, SWB_ERR_UNSUPPORTED, "accumulate is not available for the thread-per-output SpMM mapping");
   swb::CsrSpmmArgs a{rows, cols, nnz, n_rhs, row_ptr, col_idx, val, B, C};
+  a.accumulate = o->accumulate != 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int Bs = (int)o->spmm_block_size;
   cudaError_t e = cudaSuccess;

@@ -15,6 +15,7 @@ struct CsrSpmvArgs {
   const float *val;
   const float *x;
   float *y;
+  bool accumulate = false;  // add to y instead of overwriting (position mappings: no zero fill)
 };
 
 struct CsrSpmmArgs {
@@ -24,6 +25,7 @@ struct CsrSpmmArgs {
   const float *val;
   const float *B;
   float *C;
+  bool accumulate = false;  // add to C instead of overwriting
 };
 
 struct BsrSpmmArgs {

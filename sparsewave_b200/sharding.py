@@ -102,6 +102,72 @@ def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor
     return out[:n_rows]
 
 
+def split_by_column_range(shard: CsrShard, lo: int, hi: int) -> tuple[CsrShard, CsrShard]:
+    """Splits a row shard into the entries whose column lies in [lo, hi) and the rest; both keep
+    every row (possibly empty), the order of the entries inside a row and global column numbers."""
+    rows = shard.rows
+    rp = shard.row_ptr.to(torch.int64)
+    lengths = rp[1:] - rp[:-1]
+    row_of = torch.repeat_interleave(torch.arange(rows, dtype=torch.int64, device=rp.device), lengths)
+    inside = (shard.col_idx >= lo) & (shard.col_idx < hi)
+    parts = []
+    for mask in (inside, ~inside):
+        counts = torch.bincount(row_of[mask], minlength=rows)
+        ptr = torch.zeros(rows + 1, dtype=torch.int64, device=rp.device)
+        ptr[1:] = torch.cumsum(counts, 0)
+        parts.append(CsrShard(shard.rank, shard.world, shard.rows_total, shard.cols, shard.row_begin, shard.row_end,
+                              ptr.to(torch.int32), shard.col_idx[mask].contiguous(), shard.values[mask].contiguous()))
+    return parts[0], parts[1]
+
+
+class OverlappedShardedOperator:
+    """Row shard whose entries are split by column ownership: the entries in this rank's own chunk of
+    the dense operand run while the all-gather of the other chunks is in flight on a second stream, the
+    rest run afterwards and add to the same output (`accumulate`).  Needs the context's own communicator
+    (`Context.comm_init`) and a mapping that can accumulate (position mappings for SpMV, wave-per-row-tile
+    or thread-per-position for SpMM)."""
+
+    def __init__(self, ctx: api.Context, shard: CsrShard, options):
+        if getattr(ctx, "comm_world", 0) != shard.world:
+            raise ValueError("OverlappedShardedOperator needs Context.comm_init over the shard's ranks")
+        self.ctx, self.shard = ctx, shard
+        self.lo, self.hi = owned_dense_range(shard.cols, shard.world, shard.rank)
+        self.local, self.remote = split_by_column_range(shard, self.lo, self.hi)
+        base = options if isinstance(options, api.SwbOptions) else api.make_options(options or "")
+        self.opts_first = api.SwbOptions.from_buffer_copy(base)
+        self.opts_rest = api.SwbOptions.from_buffer_copy(base)
+        self.opts_rest.accumulate = 1
+        self.side = torch.cuda.Stream(device=shard.row_ptr.device)
+        self._full = None
+
+    def _run(self, owned: torch.Tensor, out, call):
+        s, world = self.shard, self.shard.world
+        chunk = dense_chunk(s.cols, world)
+        shape = (chunk * world,) + tuple(owned.shape[1:])
+        if self._full is None or tuple(self._full.shape) != shape or self._full.dtype != owned.dtype:
+            self._full = torch.zeros(shape, dtype=owned.dtype, device=owned.device)
+        full = self._full
+        main = torch.cuda.current_stream(owned.device)
+        # own chunk in place, then an in-place all-gather (NCCL leaves the own chunk alone) on the side stream
+        mine = full[s.rank * chunk:(s.rank + 1) * chunk]
+        mine[:owned.shape[0]].copy_(owned)
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            self.ctx.allgather(mine.view(-1), full.view(-1))
+        dense = full[:s.cols]
+        out = call(self.opts_first, self.local, dense, out)      # columns this rank owns: no remote data needed
+        main.wait_stream(self.side)
+        return call(self.opts_rest, self.remote, dense, out)      # the rest, added to the same output
+
+    def spmv(self, x_owned: torch.Tensor, y_local: Optional[torch.Tensor] = None):
+        return self._run(x_owned, y_local, lambda o, p, d, out: self.ctx.spmv(o, p.row_ptr, p.col_idx, p.values, d,
+                                                                             out, rows=p.rows))
+
+    def spmm(self, B_owned: torch.Tensor, C_local: Optional[torch.Tensor] = None):
+        return self._run(B_owned, C_local, lambda o, p, d, out: self.ctx.spmm(o, p.row_ptr, p.col_idx, p.values, d,
+                                                                             out, rows=p.rows))
+
+
 class ShardedOperator:
     """A row shard bound to a library context: gathers the dense operand, then
     runs the local kernel on this rank's rows."""

@@ -111,3 +111,30 @@ def test_argument_errors(ctx):
     before = ctx.kernel_launches
     ctx.spmv("mapping=wave-per-position", *t)
     assert ctx.kernel_launches == before + 2  # zero fill + compute
+
+
+def test_accumulate_option(ctx):
+    """accumulate=1 adds to the existing output (no zero fill / add on store); other mappings refuse it."""
+    rp, ci, v = random_csr(900, 400, 10, seed=5)
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-1, 1, 400).astype(np.float32)
+    B = rng.uniform(-1, 1, (400, 8)).astype(np.float32)
+    t = [dev(rp, torch.int32), dev(ci, torch.int32), dev(v), dev(x)]
+    bound = oracle.csr_abs_bound(rp, ci, v, x)
+    for opts in ("mapping=wave-per-position", "mapping=wave-per-position wave-position-batch=1",
+                 "mapping=thread-per-position thread-chunk-size=4 thread-reduction=segmented"):
+        y = ctx.spmv(opts, *t)
+        ctx.spmv(opts + " accumulate=1", *t, y)
+        assert_within_bound(y.cpu().numpy() / 2, oracle.csr_spmv(rp, ci, v, x), bound, rel=2e-5)
+    with pytest.raises(SparseWaveError, match="accumulate is available for the position mappings"):
+        ctx.spmv("mapping=wave-per-row accumulate=1", *t)
+    Bd = dev(B)
+    boundB = oracle.csr_abs_bound(rp, ci, v, B)
+    for opts in ("spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=64",
+                 "spmm-mapping=wave-per-row-tile spmm-tile-size=3 spmm-block-size=64",
+                 "spmm-mapping=thread-per-position spmm-position-chunk-size=4"):
+        Cm = ctx.spmm(opts, t[0], t[1], t[2], Bd)
+        ctx.spmm(opts + " accumulate=1", t[0], t[1], t[2], Bd, Cm)
+        assert_within_bound(Cm.cpu().numpy() / 2, oracle.csr_spmm(rp, ci, v, B), boundB, rel=2e-5)
+    with pytest.raises(SparseWaveError, match="accumulate is not available"):
+        ctx.spmm("spmm-mapping=thread-per-output accumulate=1", t[0], t[1], t[2], Bd)

@@ -44,6 +44,14 @@ def _rank_main(rank, world, port):
         C = op.spmm(B[lo:hi].contiguous()).cpu().numpy()
         bound = oracle.csr_abs_bound(rp, ci, v, Bh)[rows]
         assert np.all(np.abs(C - oracle.csr_spmm(rp, ci, v, Bh)[rows]) <= 1e-5 * bound + 1e-30)
+        # all-gather overlapped with the locally-owned columns, second part accumulated into the same output
+        ov = sharding.OverlappedShardedOperator(ctx, shard, "spmv-mapping=wave-per-position")
+        for _ in range(2):
+            y3 = ov.spmv(x[lo:hi].contiguous()).cpu().numpy()
+            assert np.all(np.abs(y3 - y) <= 2e-5 * oracle.csr_abs_bound(rp, ci, v, xh)[rows] + 1e-30)
+        ov = sharding.OverlappedShardedOperator(ctx, shard, "spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128")
+        C3 = ov.spmm(B[lo:hi].contiguous()).cpu().numpy()
+        assert np.all(np.abs(C3 - C) <= 2e-5 * bound + 1e-30)
         # shard boundaries are the same on every rank
         b = torch.tensor(sharding.shard_boundaries(a.row_ptr, world), device="cuda")
         ref = b.clone()

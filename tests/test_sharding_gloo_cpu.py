@@ -74,3 +74,19 @@ def test_dense_chunks():
     assert sharding.dense_chunk(701, 2) == 351
     assert sharding.owned_dense_range(701, 2, 1) == (351, 701)
     assert sharding.owned_dense_range(5, 8, 7) == (5, 5)
+
+
+def test_split_by_column_ownership():
+    rp, ci, v = random_csr(500, 300, 8, seed=3, empty_fraction=0.3)
+    x = np.random.default_rng(0).uniform(-1, 1, 300).astype(np.float32)
+    shard = sharding.shard_csr(torch.from_numpy(rp), torch.from_numpy(ci), torch.from_numpy(v), 300, 1, 2)
+    lo, hi = sharding.owned_dense_range(300, 2, 1)
+    own, rest = sharding.split_by_column_range(shard, lo, hi)
+    assert own.nnz + rest.nnz == shard.nnz and own.rows == rest.rows == shard.rows
+    assert bool(((own.col_idx >= lo) & (own.col_idx < hi)).all()) and bool(((rest.col_idx < lo) | (rest.col_idx >= hi)).all())
+    parts = [oracle.csr_spmv(p.row_ptr.numpy(), p.col_idx.numpy(), p.values.numpy(), x) for p in (shard, own, rest)]
+    assert np.allclose(parts[0], parts[1] + parts[2], atol=1e-5)
+    for p in (own, rest):  # order inside a row is preserved: columns stay sorted
+        r = p.row_ptr.numpy()
+        c = p.col_idx.numpy()
+        assert all(np.all(np.diff(c[r[i]:r[i + 1]]) > 0) for i in range(p.rows))
