@@ -74,7 +74,24 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
+    build_runner(verbose)
     return LIB
+
+
+RUNNER_SRC = CSRC / "runner" / "swb_runner.cpp"
+RUNNER = LIBDIR / "swb_runner"
+
+
+def build_runner(verbose: bool = False) -> Path:
+    """Native benchmark runner (C++ host program over the C ABI), linked against the library in-tree."""
+    if _stale(RUNNER, [RUNNER_SRC, LIB] + _headers()):
+        cmd = [_nvcc(), "-O2", "-std=c++17", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a",
+               str(RUNNER_SRC), "-o", str(RUNNER), "-L", str(LIBDIR), "-lsparsewave_b200",
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+    return RUNNER
 
 
 if __name__ == "__main__":
