@@ -11,6 +11,13 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    # The shared library, the runner and the oracle are build products (not in the repository):
+    # compile whatever is missing or older than its sources before any test imports them.
+    from sparsewave_b200 import build as lib_build
+    lib_build.build()
+    from oracle import build as oracle_build
+    oracle_build.build_oracle()
+    oracle_build.build_reference()
 
 
 @pytest.fixture(scope="session")
