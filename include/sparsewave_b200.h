@@ -254,6 +254,26 @@ SWB_API int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *opts,
                                    const uint16_t *block_values,
                                    const uint16_t *B, uint16_t *C);
 
+/* Matrix resident on the device, dense operands in host memory: the shape of
+ * the reference's own host programs, which copy the matrix to the device once
+ * and then call the operator in a loop (benchmark/spmv.mlir.in:37-65).
+ * swb_csr_upload checks the index arrays (as swb_check_csr_host does) and
+ * copies the matrix; the per-call functions copy x (or B) in, run the kernel,
+ * copy y (or C) out and synchronise.  The handle belongs to the context's
+ * device and is released with swb_csr_release. */
+typedef struct swb_csr_handle swb_csr_handle;
+SWB_API int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols,
+                           int64_t nnz, const int32_t *row_ptr,
+                           const int32_t *col_idx, const float *val,
+                           swb_csr_handle **out);
+SWB_API void swb_csr_release(swb_context *ctx, swb_csr_handle *matrix);
+SWB_API int swb_spmv_resident_host(swb_context *ctx, const swb_options *opts,
+                                   const swb_csr_handle *matrix,
+                                   const float *x, float *y);
+SWB_API int swb_spmm_resident_host(swb_context *ctx, const swb_options *opts,
+                                   const swb_csr_handle *matrix, int64_t n_rhs,
+                                   const float *B, float *C);
+
 /* Content checks the kernels rely on, run on HOST copies of the index arrays
  * before data is trusted: row_ptr[0] == 0, monotone, row_ptr[rows] == nnz,
  * 0 <= col < cols.  (The reference aborts on malformed benchmark inputs,

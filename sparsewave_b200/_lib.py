@@ -84,6 +84,10 @@ SIGNATURES = {
     "swb_spmv_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "swb_spmm_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_bf16_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
+    "swb_csr_upload": (C.c_int, [_CTX, _I64, _I64, _I64, _P, _P, _P, C.POINTER(C.c_void_p)]),
+    "swb_csr_release": (None, [_CTX, _P]),
+    "swb_spmv_resident_host": (C.c_int, [_CTX, _OPT, _P, _P, _P]),
+    "swb_spmm_resident_host": (C.c_int, [_CTX, _OPT, _P, _I64, _P, _P]),
     "swb_check_csr_host": (C.c_int, [_CTX, _I64, _I64, _I64, _P, _P]),
     "swb_spmv_memref": (C.c_int, [_CTX, _OPT, _P, _P, _P, _P, _P, _P]),
     "swb_spmm_memref": (C.c_int, [_CTX, _OPT, _P, _P, _P, _P, _P, _P]),

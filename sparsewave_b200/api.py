@@ -277,10 +277,46 @@ class Context:
             _host_ptr(C_out, torch.bfloat16, "C")))
         return C_out
 
+    def csr_upload(self, rows: int, cols: int, row_ptr, col_idx, val) -> "ResidentCsr":
+        """Checks and copies a host CSR matrix to the device once; returns a handle for the
+        `*_resident_host` calls (x / B in, y / C out per call)."""
+        h = C.c_void_p()
+        self._check(self._lib.swb_csr_upload(self._ctx, int(rows), int(cols), len(val),
+                                             _host_ptr(row_ptr, torch.int32, "row_ptr"),
+                                             _host_ptr(col_idx, torch.int32, "col_idx"),
+                                             _host_ptr(val, torch.float32, "val"), C.byref(h)))
+        return ResidentCsr(self, h, int(rows), int(cols))
+
     def check_csr_host(self, rows, cols, row_ptr, col_idx) -> None:
         self._check(self._lib.swb_check_csr_host(self._ctx, rows, cols, len(col_idx),
                                                  _host_ptr(row_ptr, torch.int32, "row_ptr"),
                                                  _host_ptr(col_idx, torch.int32, "col_idx")))
+
+
+class ResidentCsr:
+    """A CSR matrix kept on the device by `Context.csr_upload`."""
+
+    def __init__(self, ctx: Context, handle, rows: int, cols: int):
+        self.ctx, self._h, self.rows, self.cols = ctx, handle, rows, cols
+
+    def spmv_host(self, options, x, y):
+        o = self.ctx._opts(options)
+        self.ctx._check(self.ctx._lib.swb_spmv_resident_host(self.ctx._ctx, C.byref(o), self._h,
+                                                             _host_ptr(x, torch.float32, "x"),
+                                                             _host_ptr(y, torch.float32, "y")))
+        return y
+
+    def spmm_host(self, options, B, C_out):
+        o = self.ctx._opts(options)
+        self.ctx._check(self.ctx._lib.swb_spmm_resident_host(self.ctx._ctx, C.byref(o), self._h, int(B.shape[1]),
+                                                             _host_ptr(B, torch.float32, "B"),
+                                                             _host_ptr(C_out, torch.float32, "C")))
+        return C_out
+
+    def release(self) -> None:
+        if self._h:
+            self.ctx._lib.swb_csr_release(self.ctx._ctx, self._h)
+            self._h = None
 
 
 def bsr16_spmm_bf16_static(block_row_ptr, block_col_idx, block_values, B, C_out=None, *, wait: bool = True):

@@ -775,6 +775,88 @@ int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *o, int64_t rows,
   return SWB_OK;
 }
 
+// ---- device-resident matrices, host dense operands ------------------------------------
+
+struct swb_csr_handle {
+  int64_t rows, cols, nnz;
+  int32_t *row_ptr, *col_idx;
+  float *val;
+};
+
+int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, const int32_t *row_ptr,
+                   const int32_t *col_idx, const float *val, swb_csr_handle **out) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (!out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: out is NULL");
+  *out = nullptr;
+  st = swb_check_csr_host(ctx, rows, cols, nnz, row_ptr, col_idx);  // content is trusted from here on
+  if (st != SWB_OK) return st;
+  if (nnz > 0 && !val) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: NULL operand pointer");
+  swb_csr_handle *h = new swb_csr_handle{rows, cols, nnz, nullptr, nullptr, nullptr};
+  cudaError_t e = cudaMalloc(&h->row_ptr, (size_t)(rows + 1) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&h->col_idx, (size_t)(nnz > 0 ? nnz : 1) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&h->val, (size_t)(nnz > 0 ? nnz : 1) * 4);
+  if (e == cudaSuccess) e = cudaMemcpy(h->row_ptr, row_ptr, (size_t)(rows + 1) * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(h->col_idx, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(h->val, val, (size_t)nnz * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val);
+    delete h;
+    return cuda_fail(ctx, e, "csr upload");
+  }
+  *out = h;
+  return SWB_OK;
+}
+
+void swb_csr_release(swb_context *ctx, swb_csr_handle *h) {
+  if (!h) return;
+  if (ctx) cudaSetDevice(ctx->device);
+  cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val);
+  delete h;
+}
+
+int swb_spmv_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, const float *x, float *y) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (!h || (h->cols > 0 && !x) || (h->rows > 0 && !y))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL matrix handle or operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  st = workspace_reserve(ctx, pad256(h->cols * 4) + pad256(h->rows * 4));
+  if (st != SWB_OK) return st;
+  float *d_x = workspace_take<float>(ctx, h->cols);
+  float *d_y = workspace_take<float>(ctx, h->rows);
+  cudaStream_t s = ctx->host_stream;
+  if (h->cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_x, x, h->cols * 4, cudaMemcpyHostToDevice, s));
+  st = swb_spmv(ctx, o, h->rows, h->cols, h->nnz, h->row_ptr, h->col_idx, h->val, d_x, d_y, s);
+  if (st != SWB_OK) return st;
+  if (h->rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(y, d_y, h->rows * 4, cudaMemcpyDeviceToHost, s));
+  SWB_CUDA(ctx, cudaStreamSynchronize(s));
+  return SWB_OK;
+}
+
+int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, int64_t n_rhs,
+                           const float *B, float *C) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  if (!h || (h->cols > 0 && !B) || (h->rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL matrix handle or operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  st = workspace_reserve(ctx, pad256(h->cols * n_rhs * 4) + pad256(h->rows * n_rhs * 4));
+  if (st != SWB_OK) return st;
+  float *d_B = workspace_take<float>(ctx, h->cols * n_rhs);
+  float *d_C = workspace_take<float>(ctx, h->rows * n_rhs);
+  cudaStream_t s = ctx->host_stream;
+  if (h->cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_B, B, h->cols * n_rhs * 4, cudaMemcpyHostToDevice, s));
+  st = swb_spmm(ctx, o, h->rows, h->cols, h->nnz, n_rhs, h->row_ptr, h->col_idx, h->val, d_B, d_C, s);
+  if (st != SWB_OK) return st;
+  if (h->rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(C, d_C, h->rows * n_rhs * 4, cudaMemcpyDeviceToHost, s));
+  SWB_CUDA(ctx, cudaStreamSynchronize(s));
+  return SWB_OK;
+}
+
 // ---- memref-descriptor entry points -------------------------------------------------
 
 static swb_context *process_context() {

@@ -138,3 +138,28 @@ def test_accumulate_option(ctx):
         assert_within_bound(Cm.cpu().numpy() / 2, oracle.csr_spmm(rp, ci, v, B), boundB, rel=2e-5)
     with pytest.raises(SparseWaveError, match="accumulate is not available"):
         ctx.spmm("spmm-mapping=thread-per-output accumulate=1", t[0], t[1], t[2], Bd)
+
+
+def test_resident_matrix_host_calls(ctx):
+    """Matrix uploaded once (content-checked), dense operand in and result out per call."""
+    rp, ci, v = random_csr(3000, 2000, 9, seed=14)
+    rng = np.random.default_rng(14)
+    m = ctx.csr_upload(3000, 2000, rp, ci, v)
+    for seed in (1, 2):  # two different x through the same resident matrix
+        x = np.random.default_rng(seed).uniform(-1, 1, 2000).astype(np.float32)
+        y = np.empty(3000, np.float32)
+        m.spmv_host("mapping=wave-per-position", x, y)
+        assert_within_bound(y, oracle.csr_spmv(rp, ci, v, x), oracle.csr_abs_bound(rp, ci, v, x))
+    B = rng.uniform(-1, 1, (2000, 4)).astype(np.float32)
+    Cm = np.empty((3000, 4), np.float32)
+    m.spmm_host("spmm-mapping=wave-per-row-tile spmm-block-size=64", B, Cm)
+    assert_within_bound(Cm, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+    m.release()
+    bad = ci.copy()
+    bad[5] = 2000  # column out of range: rejected on the host before anything is copied
+    with pytest.raises(SparseWaveError, match="out of bounds for 2000 columns"):
+        ctx.csr_upload(3000, 2000, rp, bad, v)
+    badrp = rp.copy()
+    badrp[10] = badrp[11] + 1
+    with pytest.raises(SparseWaveError, match="non-decreasing"):
+        ctx.csr_upload(3000, 2000, badrp, ci, v)
