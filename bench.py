@@ -288,13 +288,14 @@ def run_ours(args):
         for _ in range(max(args.warmup, 3)):
             step()
         barrier()
-        # One step (collective + kernels) captured in a CUDA graph and replayed: the timed loop then has no
-        # per-step host work.  Workloads that need the L2 flush between steps stay on host launches, and so
-        # do steps whose all-gather goes through torch.distributed (capturing that one hung here, so it is not
+        # One step (collective + kernels) captured in a CUDA graph and replayed: a timed step is then a single
+        # graph launch with no host work between its kernels (with the L2 flush, which stays outside the
+        # event pairs, the replay sits between the two event records).  Host launches remain for
+        # steps whose all-gather goes through torch.distributed (capturing that one hung here, so it is not
         # tried); the library's own ncclAllGather is captured with the kernels.
         eager_step, launches_per_step, graph = step, None, None
         torch_collective = world > 1 and not args.replicated and args.torch_collective
-        if flush is None and not args.no_graph and not torch_collective:
+        if not args.no_graph and not torch_collective:
             try:
                 before = ctx.kernel_launches
                 g = torch.cuda.CUDAGraph()
