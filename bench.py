@@ -175,10 +175,10 @@ def host_copies(wl):
                 dense=dense.cpu().numpy())
 
 
-def time_cpu(wl, host, budget_s=20.0, max_passes=50):
-    """Passes over the whole workload until about `budget_s` seconds are spent; returns (best seconds, passes)."""
+def time_cpu(wl, host, seconds=20.0, max_passes=50):
+    """Passes over the whole workload until about `seconds` seconds are spent; returns (best seconds, passes)."""
     cpu_pass(wl, host)  # warm-up (page faults, thread pool)
-    best, passes, t_end = float("inf"), 0, time.perf_counter() + budget_s
+    best, passes, t_end = float("inf"), 0, time.perf_counter() + seconds
     while passes < 3 or (time.perf_counter() < t_end and passes < max_passes):
         t0 = time.perf_counter()
         cpu_pass(wl, host)

@@ -163,3 +163,39 @@ def test_resident_matrix_host_calls(ctx):
     badrp[10] = badrp[11] + 1
     with pytest.raises(SparseWaveError, match="non-decreasing"):
         ctx.csr_upload(3000, 2000, badrp, ci, v)
+
+
+def test_unaligned_operands_take_the_scalar_kernels(ctx):
+    """Operands that are not 16-byte aligned (views at an odd offset) must not reach the 128-bit paths."""
+    rng = np.random.default_rng(8)
+    lens = np.array([300, 0, 5, 700, 129, 1, 64, 4097], np.int64)
+    cols = 5000
+    rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    ci = np.concatenate([np.sort(rng.choice(cols, n, replace=False)) for n in lens]).astype(np.int32)
+    v = rng.uniform(-1, 1, rp[-1]).astype(np.float32)
+    x = rng.uniform(-1, 1, cols).astype(np.float32)
+
+    def odd(a):  # same values at a 4-byte offset from a 16-byte aligned allocation
+        t = torch.empty(len(a) + 1, dtype=torch.from_numpy(a).dtype, device="cuda")
+        t[1:] = torch.from_numpy(a).cuda()
+        return t[1:]
+
+    expected, bound = oracle.csr_spmv(rp, ci, v, x), oracle.csr_abs_bound(rp, ci, v, x)
+    for opts in ("mapping=wave-per-row block-size=128", "mapping=block-per-row block-size=64",
+                 "mapping=wave-per-position wave-position-batch=8", "mapping=wave-per-position"):
+        y = ctx.spmv(opts, dev(rp), odd(ci), odd(v), odd(x))
+        assert odd(ci).data_ptr() % 16 != 0
+        assert_within_bound(y.cpu().numpy(), expected, bound)
+    B = rng.uniform(-1, 1, (cols, 8)).astype(np.float32)
+    Bo = odd(B.reshape(-1)).view(cols, 8)
+    Cm = ctx.spmm("spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=64", dev(rp), dev(ci), dev(v), Bo)
+    assert_within_bound(Cm.cpu().numpy(), oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+    # BSR 16 x 16 with a misaligned B falls back to the CUDA-core kernel and still matches
+    from sparsewave_b200 import workloads as W
+    a = W.random_bsr(6, 5, 16, 0.5, seed=3, device="cuda")
+    Bb = W.dense_normal((80, 16), seed=3, device="cuda")
+    Bbo = torch.empty(80 * 16 + 1, dtype=torch.bfloat16, device="cuda")[1:]
+    Bbo.copy_(Bb.reshape(-1))
+    C1 = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, Bb, 16)
+    C2 = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, Bbo.view(80, 16), 16)
+    assert float((C1.float() - C2.float()).abs().max()) <= 1e-2 * float(C1.float().abs().max() + 1)
