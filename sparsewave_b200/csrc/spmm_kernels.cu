@@ -227,6 +227,61 @@ __global__ void spmm_wave_per_row_tile_vec_kernel(int64_t rows, int64_t N, int64
   }
 }
 
+// Whole rows of B of 64 or 128 floats (G = N/4 = 16 or 32 lanes per row): every tile of a matrix row is
+// computed by one warp in one pass - the (row, tile) units of a row are fused - so the row's col/val
+// stream is read once instead of once per tile and each nonzero fetches its B row as one contiguous
+// 256- or 512-byte run.  32/G lane groups stride the positions, four positions in flight per group;
+// the partial float4 sums of the groups are added with butterfly steps and group 0 stores the row of C.
+// (For N <= 32 the same fusion is the vectorised tile kernel above run with the tile widened to N.)
+template <int G>
+__global__ void spmm_wave_per_row_fused_kernel(int64_t rows, int64_t N, const int32_t *__restrict__ row_ptr,
+                                               const int32_t *__restrict__ col, const float *__restrict__ val,
+                                               const float *__restrict__ B, float *__restrict__ C,
+                                               bool accumulate) {
+  constexpr int PG = 32 / G;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int cq = lane % G, pg = lane / G;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  const float *Bt = B + 4 * cq;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto fma4 = [&](float v, const float4 &b) {
+    acc.x = add(acc.x, mul(v, b.x)); acc.y = add(acc.y, mul(v, b.y));
+    acc.z = add(acc.z, mul(v, b.z)); acc.w = add(acc.w, mul(v, b.w));
+  };
+  int p = start + pg;
+  for (; p + 3 * PG < end; p += 4 * PG) {
+    const int c0 = __ldg(col + p), c1 = __ldg(col + p + PG), c2 = __ldg(col + p + 2 * PG), c3 = __ldg(col + p + 3 * PG);
+    const float v0 = __ldg(val + p), v1 = __ldg(val + p + PG), v2 = __ldg(val + p + 2 * PG), v3 = __ldg(val + p + 3 * PG);
+    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+    const float4 b1 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c1 * N));
+    const float4 b2 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c2 * N));
+    const float4 b3 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c3 * N));
+    fma4(v0, b0); fma4(v1, b1); fma4(v2, b2); fma4(v3, b3);
+  }
+  for (; p < end; p += PG) {
+    const int c0 = __ldg(col + p);
+    const float v0 = __ldg(val + p);
+    fma4(v0, __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N)));
+  }
+#pragma unroll
+  for (int off = G; off < 32; off <<= 1) {
+    acc.x = add(acc.x, __shfl_xor_sync(FULL, acc.x, off));
+    acc.y = add(acc.y, __shfl_xor_sync(FULL, acc.y, off));
+    acc.z = add(acc.z, __shfl_xor_sync(FULL, acc.z, off));
+    acc.w = add(acc.w, __shfl_xor_sync(FULL, acc.w, off));
+  }
+  if (pg == 0) {
+    float4 *out = reinterpret_cast<float4 *>(C + row * N) + cq;
+    if (accumulate) {
+      const float4 old = *out;
+      acc.x = add(old.x, acc.x); acc.y = add(old.y, acc.y); acc.z = add(old.z, acc.z); acc.w = add(old.w, acc.w);
+    }
+    *out = acc;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // thread-per-position (DecomposePositionSpMMPattern,
 // PositionSpMMDecomposition.cpp:19-73, scheduled with the thread/atomic
@@ -300,6 +355,26 @@ cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block, cudaS
 cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int tile,
                                           cudaStream_t s, int64_t *launches) {
   ++*launches;
+  // Rows of B of 4, 8, ... 128 floats on 16-byte aligned operands: all tiles of a matrix row are fused
+  // into one warp pass (the tile size then only names the logical units, SparseWaveToGPU.cpp:1078-1084).
+  const int64_t N = a.n_rhs;
+  const bool pow2_row = N >= 4 && N <= 128 && (N & (N - 1)) == 0;
+  if (pow2_row && tile < N && aligned16(a.B) && aligned16(a.C)) {
+    if (N <= 32) {
+      if (N == 4) return launch_tile<4>(a, block, 4, s);
+      if (N == 8) return launch_tile<8>(a, block, 8, s);
+      if (N == 16) return launch_tile<16>(a, block, 16, s);
+      return launch_tile<32>(a, block, 32, s);
+    }
+    const unsigned grid = (unsigned)max1(ceil_div(a.rows, block / 32));
+    if (N == 64)
+      spmm_wave_per_row_fused_kernel<16><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,
+                                                                 a.accumulate);
+    else
+      spmm_wave_per_row_fused_kernel<32><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,
+                                                                 a.accumulate);
+    return cudaGetLastError();
+  }
   if (tile <= 1) return launch_tile<1>(a, block, tile, s);
   if (tile <= 2) return launch_tile<2>(a, block, tile, s);
   if (tile <= 4) return launch_tile<4>(a, block, tile, s);
