@@ -413,6 +413,17 @@ SWB_API int swb_shard_rows_by_nnz(swb_context *ctx, const int32_t *row_ptr,
                                   int64_t rows, int64_t n_shards,
                                   int64_t *boundaries);
 
+/* ---- row panels of a resident matrix -------------------------------------- */
+/* The cut swb_csr_upload makes for the pipelined result copy of the resident
+ * host calls: min(8, nnz / panel_nnz) contiguous row panels of about equal
+ * nnz each, every panel starting at a row whose first position is a multiple of
+ * 4 (so its col/val slices stay 16-byte aligned).  row_ptr is a HOST array of
+ * rows + 1 offsets starting at 0; panel_rows receives the first row of each
+ * panel followed by `rows` (at most 9 entries); returns the number of panels
+ * (>= 1).  Not a reference feature. */
+SWB_API int swb_plan_row_panels(int64_t rows, int64_t nnz, const int32_t *row_ptr,
+                                int64_t panel_nnz, int64_t *panel_rows);
+
 #ifdef __cplusplus
 }
 #endif

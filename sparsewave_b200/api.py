@@ -370,6 +370,17 @@ def shard_rows_by_nnz(row_ptr: np.ndarray, n_shards: int) -> np.ndarray:
     return out
 
 
+def plan_row_panels(row_ptr: np.ndarray, panel_nnz: int = 20000000) -> np.ndarray:
+    """Row panels a resident matrix is cut into for the pipelined result copy (host array of row offsets
+    in, first row of each panel followed by the row count out)."""
+    lib = _lib.load()
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    out = np.zeros(9, dtype=np.int64)
+    rows = len(row_ptr) - 1
+    count = lib.swb_plan_row_panels(rows, int(row_ptr[-1]), row_ptr.ctypes.data, int(panel_nnz), out.ctypes.data)
+    return out[:count + 1]
+
+
 def launch_shape(options, rows: int, nnz: int, n_rhs: int = 0) -> SwbLaunchShape:
     """Launch geometry without a context (auto batch assumes 148 SMs)."""
     lib = _lib.load()

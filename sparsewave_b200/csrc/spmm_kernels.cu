@@ -282,6 +282,62 @@ __global__ void spmm_wave_per_row_fused_kernel(int64_t rows, int64_t N, const in
   }
 }
 
+// Short matrix rows with rows of B of up to 32 floats: a full warp per row leaves most lanes with one
+// position or none and the kernel waits on three dependent loads per warp.  Here L = 4, 8 or 16 lanes
+// serve one matrix row (32/L rows per warp): G = N/4 adjacent lanes cover the row of B with one float4
+// each, the L/G lane groups stride the row's positions with four positions in flight, butterfly steps
+// over the lane distances G ... L/2 add the groups' partial sums, group 0 stores the row of C.
+template <int G, int L>
+__global__ void spmm_subwarp_row_kernel(int64_t rows, int64_t N, const int32_t *__restrict__ row_ptr,
+                                        const int32_t *__restrict__ col, const float *__restrict__ val,
+                                        const float *__restrict__ B, float *__restrict__ C, bool accumulate) {
+  constexpr int PG = L / G, RW = 32 / L;
+  static_assert(L >= G && L < 32 && PG >= 1, "lanes per row");
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp * RW >= rows) return;  // whole warp out of range
+  const int l = lane % L, cq = l % G, pg = l / G;
+  const int64_t row = warp * RW + lane / L;
+  const bool live = row < rows;  // lanes past the last row still take part in the shuffles
+  const int start = live ? row_ptr[row] : 0, end = live ? row_ptr[row + 1] : 0;
+  const float *Bt = B + 4 * cq;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto fma4 = [&](float v, const float4 &b) {
+    acc.x = add(acc.x, mul(v, b.x)); acc.y = add(acc.y, mul(v, b.y));
+    acc.z = add(acc.z, mul(v, b.z)); acc.w = add(acc.w, mul(v, b.w));
+  };
+  int p = start + pg;
+  for (; p + 3 * PG < end; p += 4 * PG) {
+    const int c0 = __ldg(col + p), c1 = __ldg(col + p + PG), c2 = __ldg(col + p + 2 * PG), c3 = __ldg(col + p + 3 * PG);
+    const float v0 = __ldg(val + p), v1 = __ldg(val + p + PG), v2 = __ldg(val + p + 2 * PG), v3 = __ldg(val + p + 3 * PG);
+    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+    const float4 b1 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c1 * N));
+    const float4 b2 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c2 * N));
+    const float4 b3 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c3 * N));
+    fma4(v0, b0); fma4(v1, b1); fma4(v2, b2); fma4(v3, b3);
+  }
+  for (; p < end; p += PG) {
+    const int c0 = __ldg(col + p);
+    const float v0 = __ldg(val + p);
+    fma4(v0, __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N)));
+  }
+#pragma unroll
+  for (int off = G; off < L; off <<= 1) {
+    acc.x = add(acc.x, __shfl_xor_sync(FULL, acc.x, off));
+    acc.y = add(acc.y, __shfl_xor_sync(FULL, acc.y, off));
+    acc.z = add(acc.z, __shfl_xor_sync(FULL, acc.z, off));
+    acc.w = add(acc.w, __shfl_xor_sync(FULL, acc.w, off));
+  }
+  if (live && pg == 0) {
+    float4 *out = reinterpret_cast<float4 *>(C + row * N) + cq;
+    if (accumulate) {
+      const float4 old = *out;
+      acc.x = add(old.x, acc.x); acc.y = add(old.y, acc.y); acc.z = add(old.z, acc.z); acc.w = add(old.w, acc.w);
+    }
+    *out = acc;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // thread-per-position (DecomposePositionSpMMPattern,
 // PositionSpMMDecomposition.cpp:19-73, scheduled with the thread/atomic
@@ -341,6 +397,27 @@ cudaError_t launch_tile(const CsrSpmmArgs &a, int block, int T, cudaStream_t s) 
   return cudaGetLastError();
 }
 
+template <int G, int L>
+cudaError_t launch_subwarp(const CsrSpmmArgs &a, int block, cudaStream_t s) {
+  const int64_t warps = ceil_div(a.rows, 32 / L);
+  spmm_subwarp_row_kernel<G, L><<<(unsigned)max1(ceil_div(warps, block / 32)), block, 0, s>>>(
+      a.rows, a.n_rhs, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
+  return cudaGetLastError();
+}
+
+// Lanes per matrix row for rows of B of 4*G floats: enough lane groups that each gets about four of the
+// mean row's positions, at least 4 lanes (and at least G), at most the warp.
+template <int G>
+cudaError_t launch_row_of_tiles(const CsrSpmmArgs &a, int block, cudaStream_t s) {
+  const int64_t mean = a.rows > 0 ? a.nnz / a.rows : 0;
+  int lanes = G > 4 ? G : 4;
+  while (lanes < 32 && (int64_t)(lanes / G) * 4 < mean) lanes *= 2;
+  if constexpr (G <= 4) if (lanes == 4) return launch_subwarp<G, 4>(a, block, s);
+  if constexpr (G <= 8) if (lanes == 8) return launch_subwarp<G, 8>(a, block, s);
+  if (lanes == 16) return launch_subwarp<G, 16>(a, block, s);
+  return launch_tile<4 * G>(a, block, 4 * G, s);
+}
+
 }  // namespace
 
 cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block, cudaStream_t s,
@@ -356,16 +433,15 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
                                           cudaStream_t s, int64_t *launches) {
   ++*launches;
   // Rows of B of 4, 8, ... 128 floats on 16-byte aligned operands: all tiles of a matrix row are fused
-  // into one warp pass (the tile size then only names the logical units, SparseWaveToGPU.cpp:1078-1084).
+  // into one pass (the tile size then only names the logical units, SparseWaveToGPU.cpp:1078-1084), by a
+  // warp, or by part of a warp where the rows are short.
   const int64_t N = a.n_rhs;
   const bool pow2_row = N >= 4 && N <= 128 && (N & (N - 1)) == 0;
-  if (pow2_row && tile < N && aligned16(a.B) && aligned16(a.C)) {
-    if (N <= 32) {
-      if (N == 4) return launch_tile<4>(a, block, 4, s);
-      if (N == 8) return launch_tile<8>(a, block, 8, s);
-      if (N == 16) return launch_tile<16>(a, block, 16, s);
-      return launch_tile<32>(a, block, 32, s);
-    }
+  if (pow2_row && aligned16(a.B) && aligned16(a.C)) {
+    if (N == 4) return launch_row_of_tiles<1>(a, block, s);
+    if (N == 8) return launch_row_of_tiles<2>(a, block, s);
+    if (N == 16) return launch_row_of_tiles<4>(a, block, s);
+    if (N == 32) return launch_row_of_tiles<8>(a, block, s);
     const unsigned grid = (unsigned)max1(ceil_div(a.rows, block / 32));
     if (N == 64)
       spmm_wave_per_row_fused_kernel<16><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,

@@ -24,6 +24,9 @@ struct swb_context {
   size_t workspace_bytes = 0;
   size_t workspace_used = 0;
   cudaStream_t host_stream = nullptr;
+  // Result copies of the resident-matrix host calls run here, behind the kernels of later row panels.
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t panel_done[8] = {};
   int *status_flag = nullptr;  // device int for kernels with bounded waits
   void *comm = nullptr;        // NCCL communicator of the multi-GPU path (swb_comm.cu)
   int comm_ranks = 1, comm_rank = 0;
@@ -154,6 +157,23 @@ int ensure_host_stream(swb_context *ctx) {
   return SWB_OK;
 }
 
+int ensure_copy_stream(swb_context *ctx) {
+  if (ctx->copy_stream) return SWB_OK;
+  cudaError_t e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
+  for (int k = 0; e == cudaSuccess && k < 8; ++k)
+    e = cudaEventCreateWithFlags(&ctx->panel_done[k], cudaEventDisableTiming);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamCreate(copy)");
+  return SWB_OK;
+}
+
+int64_t env_i64(const char *name, int64_t fallback) {
+  const char *text = getenv(name);
+  if (!text || !*text) return fallback;
+  char *end = nullptr;
+  long long v = strtoll(text, &end, 10);
+  return (*end == '\0' && v > 0) ? v : fallback;
+}
+
 #define SWB_CUDA(ctx, call)                                   \
   do {                                                        \
     cudaError_t e__ = (call);                                 \
@@ -210,6 +230,9 @@ void swb_destroy(swb_context *ctx) {
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->status_flag) cudaFree(ctx->status_flag);
   if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+  if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+  for (cudaEvent_t ev : ctx->panel_done)
+    if (ev) cudaEventDestroy(ev);
   delete ctx;
 }
 
@@ -777,11 +800,68 @@ int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *o, int64_t rows,
 
 // ---- device-resident matrices, host dense operands ------------------------------------
 
+// Row panels of a resident matrix.  The host calls below copy the result back to the host while later
+// rows are still being computed: the rows are cut into up to 8 contiguous panels of about equal nnz, each
+// panel is launched as a CSR problem of its own (its row offsets rebased to zero and stored once at upload,
+// its slice of col/val, the whole dense operand, its rows of the output) and its rows of the result start
+// their device-to-host copy on a second stream as soon as its kernels are done.  A panel starts at a row
+// whose first position is a multiple of 4 (of 32 where one is near), so the col/val slices keep the
+// 16-byte alignment the vectorised kernels ask for.  Environment: SWB_RESIDENT_PANEL_NNZ (nnz per panel
+// that makes a matrix worth cutting, default 20000000) and SWB_RESIDENT_PANEL_BYTES (result bytes per
+// panel below which a call runs uncut, default 524288), both read at upload.
+constexpr int kMaxPanels = 8;
+
 struct swb_csr_handle {
   int64_t rows, cols, nnz;
   int32_t *row_ptr, *col_idx;
   float *val;
+  int panels = 1;
+  int64_t panel_row[kMaxPanels + 1] = {};     // first row of each panel, then rows
+  int64_t panel_pos[kMaxPanels + 1] = {};     // row_ptr[panel_row[k]]
+  int64_t panel_rp_off[kMaxPanels] = {};      // start of panel k's rebased row offsets inside panel_row_ptr
+  int32_t *panel_row_ptr = nullptr;           // device
+  int64_t panel_min_bytes = 0;
 };
+
+namespace {
+
+// Panel boundaries on the host: boundary k is the first row at or after the nnz-balanced cut whose first
+// position is aligned, looked for in a bounded window; a cut without one, or one that repeats the
+// previous boundary, is dropped.
+int plan_panels(int64_t rows, int64_t nnz, const int32_t *row_ptr, int64_t panel_nnz, int64_t *panel_row) {
+  int64_t want = nnz / panel_nnz;
+  if (want > kMaxPanels) want = kMaxPanels;
+  panel_row[0] = 0;
+  int count = 0;
+  for (int64_t k = 1; k < want; ++k) {
+    const int64_t target = (int64_t)((__int128)nnz * k / want);
+    int64_t lo = 0, hi = rows;  // first row with row_ptr[row] >= target
+    while (lo < hi) {
+      const int64_t mid = lo + (hi - lo) / 2;
+      if (row_ptr[mid] < target) lo = mid + 1; else hi = mid;
+    }
+    const int64_t window = lo + 4096 < rows ? lo + 4096 : rows;
+    int64_t pick = -1;
+    for (int64_t r = lo; r < window; ++r)
+      if (row_ptr[r] % 32 == 0) { pick = r; break; }
+    for (int64_t r = lo; pick < 0 && r < window; ++r)
+      if (row_ptr[r] % 4 == 0) pick = r;
+    if (pick <= panel_row[count] || pick >= rows) continue;
+    panel_row[++count] = pick;
+  }
+  panel_row[++count] = rows;
+  return count;
+}
+
+}  // namespace
+
+int swb_plan_row_panels(int64_t rows, int64_t nnz, const int32_t *row_ptr, int64_t panel_nnz, int64_t *panel_rows) {
+  if (!panel_rows) return 0;
+  panel_rows[0] = 0;
+  panel_rows[1] = rows > 0 ? rows : 0;
+  if (rows <= 0 || nnz <= 0 || !row_ptr || panel_nnz <= 0) return 1;
+  return plan_panels(rows, nnz, row_ptr, panel_nnz, panel_rows);
+}
 
 int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, const int32_t *row_ptr,
                    const int32_t *col_idx, const float *val, swb_csr_handle **out) {
@@ -792,15 +872,39 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
   st = swb_check_csr_host(ctx, rows, cols, nnz, row_ptr, col_idx);  // content is trusted from here on
   if (st != SWB_OK) return st;
   if (nnz > 0 && !val) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: NULL operand pointer");
-  swb_csr_handle *h = new swb_csr_handle{rows, cols, nnz, nullptr, nullptr, nullptr};
+  swb_csr_handle *h = new swb_csr_handle();
+  h->rows = rows; h->cols = cols; h->nnz = nnz;
+  h->row_ptr = h->col_idx = nullptr; h->val = nullptr;
   cudaError_t e = cudaMalloc(&h->row_ptr, (size_t)(rows + 1) * 4);
   if (e == cudaSuccess) e = cudaMalloc(&h->col_idx, (size_t)(nnz > 0 ? nnz : 1) * 4);
   if (e == cudaSuccess) e = cudaMalloc(&h->val, (size_t)(nnz > 0 ? nnz : 1) * 4);
   if (e == cudaSuccess) e = cudaMemcpy(h->row_ptr, row_ptr, (size_t)(rows + 1) * 4, cudaMemcpyHostToDevice);
   if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(h->col_idx, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice);
   if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(h->val, val, (size_t)nnz * 4, cudaMemcpyHostToDevice);
+
+  // Row panels for the pipelined result copy.
+  h->panel_min_bytes = env_i64("SWB_RESIDENT_PANEL_BYTES", 512 * 1024);
+  h->panel_row[1] = rows;
+  h->panel_pos[1] = nnz;
+  if (e == cudaSuccess && rows > 0 && nnz > 0) {
+    const int count = plan_panels(rows, nnz, row_ptr, env_i64("SWB_RESIDENT_PANEL_NNZ", 20000000), h->panel_row);
+    if (count > 1) {
+      std::vector<int32_t> rebased;
+      for (int k = 0; k < count; ++k) {
+        const int64_t r0 = h->panel_row[k], r1 = h->panel_row[k + 1];
+        h->panel_pos[k] = row_ptr[r0];
+        h->panel_rp_off[k] = (int64_t)rebased.size();
+        for (int64_t r = r0; r <= r1; ++r) rebased.push_back(row_ptr[r] - row_ptr[r0]);
+        while (rebased.size() % 64) rebased.push_back(0);  // every panel's offsets start 256-byte aligned
+      }
+      h->panel_pos[count] = nnz;
+      e = cudaMalloc(&h->panel_row_ptr, rebased.size() * 4);
+      if (e == cudaSuccess) e = cudaMemcpy(h->panel_row_ptr, rebased.data(), rebased.size() * 4, cudaMemcpyHostToDevice);
+      if (e == cudaSuccess) h->panels = count;
+    }
+  }
   if (e != cudaSuccess) {
-    cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val);
+    cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val); cudaFree(h->panel_row_ptr);
     delete h;
     return cuda_fail(ctx, e, "csr upload");
   }
@@ -811,28 +915,73 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
 void swb_csr_release(swb_context *ctx, swb_csr_handle *h) {
   if (!h) return;
   if (ctx) cudaSetDevice(ctx->device);
-  cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val);
+  cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val); cudaFree(h->panel_row_ptr);
   delete h;
 }
+
+extern "C++" {
+namespace {
+
+// Shared body of the two resident host calls.  `width` = floats per row of the dense operand and of the
+// result (1 for SpMV); `launch(rows, nnz, row_ptr, col, val, out)` queues one operator call on the
+// host stream.
+template <typename Launch>
+int resident_host_call(swb_context *ctx, const swb_csr_handle *h, int64_t width, const float *dense_host,
+                       float *out_host, float **d_dense_out, Launch launch) {
+  int st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  const size_t dense_bytes = (size_t)h->cols * width * 4, out_bytes = (size_t)h->rows * width * 4;
+  st = workspace_reserve(ctx, pad256(dense_bytes) + pad256(out_bytes));
+  if (st != SWB_OK) return st;
+  float *d_dense = workspace_take<float>(ctx, h->cols * width);
+  float *d_out = workspace_take<float>(ctx, h->rows * width);
+  *d_dense_out = d_dense;
+  cudaStream_t s = ctx->host_stream;
+  if (dense_bytes > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_dense, dense_host, dense_bytes, cudaMemcpyHostToDevice, s));
+  const bool cut = h->panels > 1 && (int64_t)(out_bytes / h->panels) >= h->panel_min_bytes;
+  if (!cut) {
+    st = launch(h->rows, h->nnz, h->row_ptr, h->col_idx, h->val, d_out);
+    if (st != SWB_OK) return st;
+    if (out_bytes > 0) SWB_CUDA(ctx, cudaMemcpyAsync(out_host, d_out, out_bytes, cudaMemcpyDeviceToHost, s));
+    SWB_CUDA(ctx, cudaStreamSynchronize(s));
+    return SWB_OK;
+  }
+  st = ensure_copy_stream(ctx);
+  if (st != SWB_OK) return st;
+  cudaError_t e = cudaSuccess;
+  for (int k = 0; k < h->panels && st == SWB_OK && e == cudaSuccess; ++k) {
+    const int64_t r0 = h->panel_row[k], r1 = h->panel_row[k + 1], p0 = h->panel_pos[k];
+    st = launch(r1 - r0, h->panel_pos[k + 1] - p0, h->panel_row_ptr + h->panel_rp_off[k], h->col_idx + p0,
+                h->val + p0, d_out + r0 * width);
+    if (st != SWB_OK) break;
+    e = cudaEventRecord(ctx->panel_done[k], s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy_stream, ctx->panel_done[k], 0);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(out_host + r0 * width, d_out + r0 * width, (size_t)(r1 - r0) * width * 4,
+                          cudaMemcpyDeviceToHost, ctx->copy_stream);
+  }
+  // Both streams are drained before returning, also after an error: the copies write caller memory.
+  const cudaError_t e1 = cudaStreamSynchronize(s), e2 = cudaStreamSynchronize(ctx->copy_stream);
+  if (st != SWB_OK) return st;
+  if (e == cudaSuccess) e = e1 != cudaSuccess ? e1 : e2;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "resident host call");
+  return SWB_OK;
+}
+
+}  // namespace
+}  // extern "C++"
 
 int swb_spmv_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, const float *x, float *y) {
   int st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   if (!h || (h->cols > 0 && !x) || (h->rows > 0 && !y))
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL matrix handle or operand pointer");
-  st = ensure_host_stream(ctx);
-  if (st != SWB_OK) return st;
-  st = workspace_reserve(ctx, pad256(h->cols * 4) + pad256(h->rows * 4));
-  if (st != SWB_OK) return st;
-  float *d_x = workspace_take<float>(ctx, h->cols);
-  float *d_y = workspace_take<float>(ctx, h->rows);
-  cudaStream_t s = ctx->host_stream;
-  if (h->cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_x, x, h->cols * 4, cudaMemcpyHostToDevice, s));
-  st = swb_spmv(ctx, o, h->rows, h->cols, h->nnz, h->row_ptr, h->col_idx, h->val, d_x, d_y, s);
-  if (st != SWB_OK) return st;
-  if (h->rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(y, d_y, h->rows * 4, cudaMemcpyDeviceToHost, s));
-  SWB_CUDA(ctx, cudaStreamSynchronize(s));
-  return SWB_OK;
+  float *d_x = nullptr;
+  return resident_host_call(ctx, h, 1, x, y, &d_x,
+                            [&](int64_t rows, int64_t nnz, const int32_t *rp, const int32_t *ci, const float *v,
+                                float *d_y) {
+                              return swb_spmv(ctx, o, rows, h->cols, nnz, rp, ci, v, d_x, d_y, ctx->host_stream);
+                            });
 }
 
 int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, int64_t n_rhs,
@@ -842,19 +991,13 @@ int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr
   if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
   if (!h || (h->cols > 0 && !B) || (h->rows > 0 && !C))
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL matrix handle or operand pointer");
-  st = ensure_host_stream(ctx);
-  if (st != SWB_OK) return st;
-  st = workspace_reserve(ctx, pad256(h->cols * n_rhs * 4) + pad256(h->rows * n_rhs * 4));
-  if (st != SWB_OK) return st;
-  float *d_B = workspace_take<float>(ctx, h->cols * n_rhs);
-  float *d_C = workspace_take<float>(ctx, h->rows * n_rhs);
-  cudaStream_t s = ctx->host_stream;
-  if (h->cols > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_B, B, h->cols * n_rhs * 4, cudaMemcpyHostToDevice, s));
-  st = swb_spmm(ctx, o, h->rows, h->cols, h->nnz, n_rhs, h->row_ptr, h->col_idx, h->val, d_B, d_C, s);
-  if (st != SWB_OK) return st;
-  if (h->rows > 0) SWB_CUDA(ctx, cudaMemcpyAsync(C, d_C, h->rows * n_rhs * 4, cudaMemcpyDeviceToHost, s));
-  SWB_CUDA(ctx, cudaStreamSynchronize(s));
-  return SWB_OK;
+  float *d_B = nullptr;
+  return resident_host_call(ctx, h, n_rhs, B, C, &d_B,
+                            [&](int64_t rows, int64_t nnz, const int32_t *rp, const int32_t *ci, const float *v,
+                                float *d_C) {
+                              return swb_spmm(ctx, o, rows, h->cols, nnz, n_rhs, rp, ci, v, d_B, d_C,
+                                              ctx->host_stream);
+                            });
 }
 
 // ---- memref-descriptor entry points -------------------------------------------------
@@ -1005,7 +1148,8 @@ int swb_bundle_launch(swb_context *ctx, const char *operation, int64_t n, void *
   // tile 4, N == 4 (tools/sparsewave-bundle/sparsewave_bundle_ir.py:4-9).
   // The bundle kernel takes bare pointers, so the reduction extent (rows of
   // rhs) and NNZ are not part of the contract; they only matter for argument
-  // checks here and are passed as upper bounds.
+  // checks here and are passed as upper bounds (with that NNZ the launcher
+  // keeps a whole warp per row, the schedule the contract names).
   swb_options o;
   swb_options_default(&o);
   o.spmm_mapping = SWB_WAVE_PER_ROW_TILE;

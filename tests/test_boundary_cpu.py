@@ -177,3 +177,30 @@ def test_compute_fails_loudly_without_a_device():
     with pytest.raises(swb.SparseWaveError) as e:
         swb.Context(0)
     assert e.value.status == _lib.SWB_ERR_CUDA
+
+
+def test_plan_row_panels():
+    """Row panels of a resident matrix: contiguous, strictly increasing, aligned first positions, about
+    equal nnz; no cut where no row starts at an aligned position or the matrix is small."""
+    from sparsewave_b200.api import plan_row_panels
+    rng = np.random.default_rng(5)
+    lens = rng.integers(0, 40, 20000)
+    rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    nnz = int(rp[-1])
+    cuts = plan_row_panels(rp, nnz // 8)
+    assert cuts[0] == 0 and cuts[-1] == 20000 and len(cuts) == 9
+    assert np.all(np.diff(cuts) > 0)
+    assert all(rp[c] % 4 == 0 for c in cuts[1:-1])
+    per_panel = np.diff(rp[cuts])
+    assert per_panel.max() < 1.2 * nnz / 8 and per_panel.min() > 0.8 * nnz / 8
+    assert len(plan_row_panels(rp, nnz // 3)) == 4               # nnz / panel_nnz panels
+    assert list(plan_row_panels(rp, nnz)) == [0, 20000]           # too small to cut
+    assert list(plan_row_panels(rp, 10 * nnz)) == [0, 20000]
+    # every interior row starts at position 1 mod 4: nothing to cut at
+    odd = np.concatenate([[0, 1], 1 + 4 * np.arange(1, 5000)]).astype(np.int32)
+    assert list(plan_row_panels(odd, 100)) == [0, 5000]
+    # one giant row holds most positions: the cuts that fall inside it collapse
+    giant = np.concatenate([[0], np.cumsum([8] * 10 + [100000] + [8] * 10)]).astype(np.int32)
+    cuts = plan_row_panels(giant, 1000)
+    assert cuts[0] == 0 and cuts[-1] == 21 and np.all(np.diff(cuts) > 0)
+    assert list(plan_row_panels(np.zeros(1, np.int32), 4)) == [0, 0]  # no rows

@@ -165,6 +165,48 @@ def test_resident_matrix_host_calls(ctx):
         ctx.csr_upload(3000, 2000, badrp, ci, v)
 
 
+ALL_SPMV = ["mapping=thread-per-row", "mapping=wave-per-row block-size=128", "mapping=block-per-row block-size=64",
+            "mapping=thread-per-position spmv-position-chunk-size=4",
+            "mapping=thread-per-position spmv-position-reduction=segmented spmv-position-chunk-size=8",
+            "mapping=wave-per-position", "mapping=wave-per-position wave-position-batch=1"]
+
+
+def test_resident_matrix_row_panels(ctx, monkeypatch):
+    """A resident matrix cut into row panels (result rows copied out while later panels run) gives the
+    result of the uncut call: every SpMV mapping, SpMM with aligned and ragged widths, rows of very
+    different lengths and empty rows around the cuts."""
+    from sparsewave_b200.api import plan_row_panels
+    monkeypatch.setenv("SWB_RESIDENT_PANEL_NNZ", "2000")
+    monkeypatch.setenv("SWB_RESIDENT_PANEL_BYTES", "1")
+    rng = np.random.default_rng(21)
+    rows, cols = 4000, 3000
+    lens = rng.integers(0, 12, rows)
+    lens[rng.integers(0, rows, 40)] = 0
+    lens[[7, 1500, 3999]] = [900, 2500, 333]
+    rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    ci = np.concatenate([np.sort(rng.choice(cols, n, replace=False)) for n in lens]).astype(np.int32)
+    v = rng.uniform(-1, 1, rp[-1]).astype(np.float32)
+    cuts = plan_row_panels(rp, 2000)
+    assert len(cuts) - 1 == 8 and all(rp[c] % 4 == 0 for c in cuts[1:-1])
+    m = ctx.csr_upload(rows, cols, rp, ci, v)
+    x = rng.uniform(-1, 1, cols).astype(np.float32)
+    want, bound = oracle.csr_spmv(rp, ci, v, x), oracle.csr_abs_bound(rp, ci, v, x)
+    for opt in ALL_SPMV:
+        y = np.full(rows, np.nan, np.float32)
+        m.spmv_host(opt, x, y)
+        assert_within_bound(y, want, bound)
+        if "thread-per-row" in opt:
+            assert np.array_equal(y, want)  # the sequential mapping is bit-exact, cut or not
+    for n in (1, 4, 5, 64):
+        B = rng.uniform(-1, 1, (cols, n)).astype(np.float32)
+        for opt in ("spmm-mapping=thread-per-output", "spmm-mapping=wave-per-row-tile spmm-tile-size=4",
+                    "spmm-mapping=thread-per-position spmm-position-chunk-size=3"):
+            Cm = np.full((rows, n), np.nan, np.float32)
+            m.spmm_host(opt, B, Cm)
+            assert_within_bound(Cm, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+    m.release()
+
+
 def test_unaligned_operands_take_the_scalar_kernels(ctx):
     """Operands that are not 16-byte aligned (views at an odd offset) must not reach the 128-bit paths."""
     rng = np.random.default_rng(8)
