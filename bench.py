@@ -208,11 +208,19 @@ def run_ours(args):
     opts = make_options(options)  # parsed once; the steps pass the option block
     wl = build_workload(args.workload, device, args.rows)
     kind, a, dense = wl["kind"], wl["a"], wl["dense"]
-    if kind == "bsr" and world > 1:
-        raise SystemExit("the BSR workload runs on one GPU")
 
     # ---- this rank's share --------------------------------------------------------------
-    if world > 1:
+    if world > 1 and kind == "bsr":
+        # block rows sharded by block count, bf16 B all-gathered (launch-sized at this configuration)
+        shard = sharding.shard_bsr(a.block_row_ptr, a.block_col_idx, a.block_values, a.cols, 16, rank, world)
+        op = sharding.ShardedBsrOperator(ctx, shard, opts)
+        lo, hi = sharding.owned_dense_range(a.cols, world, rank)
+        owned = dense[lo:hi].contiguous()
+        out = torch.empty((shard.rows, dense.shape[1]), dtype=torch.bfloat16, device=device)
+        full = dense if args.replicated else None
+        step = lambda: op.spmm(owned, out, replicated_B=full)
+        local_input_bytes = 512 * shard.nnzb + dense.numel() * 2
+    elif world > 1:
         shard = sharding.shard_csr(a.row_ptr, a.col_idx, a.values, a.cols, rank, world)
         overlap = args.overlap and not args.replicated and not args.torch_collective
         op = sharding.OverlappedShardedOperator(ctx, shard, opts) if overlap else \
@@ -427,8 +435,12 @@ def run_e2e(args, ctx, wl, options, rank, world, device, barrier, max_over_ranks
     steps = max(1, min(args.steps, 10))
     timer = "host clock around the synchronous C-ABI calls, max over ranks"
     if kind == "bsr":
-        h = [pin(a.block_row_ptr), pin(a.block_col_idx), pin(a.block_values), pin(dense)]
-        out = torch.empty((a.rows, dense.shape[1]), dtype=torch.bfloat16).pin_memory()
+        brp, bci, bv, rows = a.block_row_ptr, a.block_col_idx, a.block_values, a.rows
+        if world > 1:
+            s = sharding.shard_bsr(brp, bci, bv, a.cols, 16, rank, world)
+            brp, bci, bv, rows = s.block_row_ptr, s.block_col_idx, s.block_values, s.rows
+        h = [pin(brp), pin(bci), pin(bv), pin(dense)]
+        out = torch.empty((rows, dense.shape[1]), dtype=torch.bfloat16).pin_memory()
         ms = measure(lambda: ctx.bsr_spmm_bf16_host(options, h[0], h[1], h[2], h[3], 16, out), steps)
         return {"value": wl["bytes"] / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "steps": steps,
                 "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in h)),

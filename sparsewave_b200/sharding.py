@@ -76,6 +76,50 @@ def shard_csr(row_ptr: torch.Tensor, col_idx: torch.Tensor, values: torch.Tensor
                     values[p0:p1].contiguous())
 
 
+@dataclass
+class BsrShard:
+    """Block rows [block_row_begin, block_row_end) of a BSR matrix, block-row offsets rebased to zero."""
+    rank: int
+    world: int
+    cols: int
+    block_size: int
+    block_row_begin: int
+    block_row_end: int
+    block_row_ptr: torch.Tensor
+    block_col_idx: torch.Tensor
+    block_values: torch.Tensor  # flat [nnzb * bs * bs], row-major inside a block
+
+    @property
+    def rows(self) -> int:
+        return (self.block_row_end - self.block_row_begin) * self.block_size
+
+    @property
+    def row_begin(self) -> int:
+        return self.block_row_begin * self.block_size
+
+    @property
+    def row_end(self) -> int:
+        return self.block_row_end * self.block_size
+
+    @property
+    def nnzb(self) -> int:
+        return int(self.block_col_idx.numel())
+
+
+def shard_bsr(block_row_ptr: torch.Tensor, block_col_idx: torch.Tensor, block_values: torch.Tensor, cols: int,
+              block_size: int, rank: int, world: int, boundaries: Optional[np.ndarray] = None) -> BsrShard:
+    """Cuts rank's block rows out of the full BSR matrix: contiguous block rows balanced by the number of
+    blocks (the same boundary rule as the CSR shards, applied to the block-row offsets)."""
+    if boundaries is None:
+        boundaries = shard_boundaries(block_row_ptr, world)
+    r0, r1 = int(boundaries[rank]), int(boundaries[rank + 1])
+    p0, p1 = int(block_row_ptr[r0]), int(block_row_ptr[r1])
+    per_block = block_size * block_size
+    local_ptr = (block_row_ptr[r0:r1 + 1] - p0).to(torch.int32).contiguous()
+    return BsrShard(rank, world, cols, block_size, r0, r1, local_ptr, block_col_idx[p0:p1].contiguous(),
+                    block_values.reshape(-1)[p0 * per_block:p1 * per_block].contiguous())
+
+
 def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor] = None, group=None,
                     ctx: Optional[api.Context] = None) -> torch.Tensor:
     """Gathers every rank's chunk of the dense operand (leading dimension split
@@ -195,3 +239,25 @@ class ShardedOperator:
         s = self.shard
         B = replicated_B if replicated_B is not None else self._gather(B_owned, s.cols)
         return self.ctx.spmm(self.options, s.row_ptr, s.col_idx, s.values, B, C_local, rows=s.rows)
+
+
+class ShardedBsrOperator:
+    """A block-row shard of a BSR matrix bound to a library context: gathers the dense operand, then runs
+    the BSR SpMM on this rank's block rows (f32 or bf16 by the dtype of the block values)."""
+
+    def __init__(self, ctx: api.Context, shard: BsrShard, options="", group=None):
+        self.ctx, self.shard, self.options, self.group = ctx, shard, options, group
+        self._full = None
+
+    def spmm(self, B_owned: torch.Tensor, C_local: Optional[torch.Tensor] = None, *, replicated_B=None):
+        s = self.shard
+        if replicated_B is not None:
+            B = replicated_B
+        else:
+            chunk = dense_chunk(s.cols, s.world)
+            shape = (chunk * s.world,) + tuple(B_owned.shape[1:])
+            if self._full is None or tuple(self._full.shape) != shape or self._full.dtype != B_owned.dtype:
+                self._full = torch.empty(shape, dtype=B_owned.dtype, device=B_owned.device)
+            B = allgather_dense(B_owned, s.cols, self._full, self.group, self.ctx)
+        return self.ctx.bsr_spmm(self.options, s.block_row_ptr, s.block_col_idx, s.block_values, B, s.block_size,
+                                 C_local)

@@ -52,6 +52,13 @@ def _rank_main(rank, world, port):
         ov = sharding.OverlappedShardedOperator(ctx, shard, "spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128")
         C3 = ov.spmm(B[lo:hi].contiguous()).cpu().numpy()
         assert np.all(np.abs(C3 - C) <= 2e-5 * bound + 1e-30)
+        # BSR: block rows sharded by block count, bf16 B all-gathered, tensor-core kernel on the shard
+        bsr, Bb = W.config_c5(device="cuda", block_grid=64, n_rhs=128)
+        bshard = sharding.shard_bsr(bsr.block_row_ptr, bsr.block_col_idx, bsr.block_values, bsr.cols, 16, rank, world)
+        blo, bhi = sharding.owned_dense_range(bsr.cols, world, rank)
+        Cb = sharding.ShardedBsrOperator(ctx, bshard).spmm(Bb[blo:bhi].contiguous())
+        whole = ctx.bsr_spmm("", bsr.block_row_ptr, bsr.block_col_idx, bsr.block_values, Bb, 16)
+        assert torch.equal(Cb, whole[bshard.row_begin:bshard.row_end])
         # shard boundaries are the same on every rank
         b = torch.tensor(sharding.shard_boundaries(a.row_ptr, world), device="cuda")
         ref = b.clone()

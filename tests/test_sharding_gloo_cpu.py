@@ -56,6 +56,39 @@ def test_two_rank_sharded_spmv_spmm():
     assert abs(r[0][2] - total / 2) <= 64  # nnz-balanced up to one row
 
 
+def _bsr_rank_main(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sparsewave_b200 import workloads as W
+        a = W.random_bsr(37, 29, 4, 0.2, seed=8, dtype=torch.float32)
+        B = W.dense_uniform((a.cols, 6), seed=8)
+        shard = sharding.shard_bsr(a.block_row_ptr, a.block_col_idx, a.block_values, a.cols, 4, rank, world)
+        lo, hi = sharding.owned_dense_range(a.cols, world, rank)
+        B_full = sharding.allgather_dense(B[lo:hi].contiguous(), a.cols)
+        assert torch.equal(B_full, B)
+        full = oracle.bsr_spmm_f32(a.block_row_ptr.numpy(), a.block_col_idx.numpy(), a.block_values.numpy(),
+                                   B.numpy(), 4)
+        mine = oracle.bsr_spmm_f32(shard.block_row_ptr.numpy(), shard.block_col_idx.numpy(),
+                                   shard.block_values.numpy(), B_full.numpy(), 4)
+        assert np.array_equal(mine, full[shard.row_begin:shard.row_end])
+        results[rank] = (shard.block_row_begin, shard.block_row_end, shard.nnzb, shard.rows)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_bsr():
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_bsr_rank_main, args=(world, port, results), nprocs=world, join=True)
+        r = dict(results)
+    assert r[0][0] == 0 and r[0][1] == r[1][0] and r[1][1] == 37
+    assert r[0][3] + r[1][3] == 37 * 4
+    assert abs(r[0][2] - r[1][2]) <= 2 * 29  # balanced by blocks up to one block row
+
+
 def test_boundaries_are_deterministic_and_cover_rows():
     rp, _, _ = random_csr(5000, 100, 12, seed=5)
     for world in (1, 2, 4, 8):
