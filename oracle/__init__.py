@@ -220,6 +220,16 @@ def reference_csr_spmv(csr_file: Path, rows, cols, nnz):
     return rp, ci, v, x, y
 
 
+def reference_coo_spmv(coo_file: Path, rows, cols, nnz):
+    """Runs loadCOOSpMVBenchmarkInputs: returns (row, col, val, x == 1, expected)."""
+    ri, ci = np.empty(nnz, np.int32), np.empty(nnz, np.int32)
+    v, x, y = np.empty(nnz, np.float32), np.empty(cols, np.float32), np.empty(rows, np.float32)
+    os.environ["SPARSEWAVE_BENCHMARK_COO"] = str(coo_file)
+    d = [_m1(a) for a in (ri, ci, v, x, y)]
+    _reflib()._mlir_ciface_loadCOOSpMVBenchmarkInputs(*[C.byref(m) for m in d])
+    return ri, ci, v, x, y
+
+
 def reference_csr_spmm(csr_file: Path, rows, cols, nnz, n):
     """Runs loadSpMMBenchmarkInputs: returns (row_ptr, col, val, B pattern, expected)."""
     rp, ci, v = np.empty(rows + 1, np.int32), np.empty(nnz, np.int32), np.empty(nnz, np.float32)

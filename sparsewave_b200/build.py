@@ -75,6 +75,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
     build_runner(verbose)
+    build_loaders(verbose)
     return LIB
 
 
@@ -92,6 +93,24 @@ def build_runner(verbose: bool = False) -> Path:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
     return RUNNER
+
+
+LOADER_SRCS = sorted((CSRC / "loaders").glob("*.cpp"))
+LOADERS = LIBDIR / "libsparsewave_benchmark_utils.so"
+
+
+def build_loaders(verbose: bool = False) -> Path:
+    """Host-only input loaders and Matrix Market converter (g++; no CUDA): the stand-in for the reference's
+    libsparsewave_benchmark_utils.so.  No contraction of a*b+c, so that the expected outputs are the plain
+    single-precision loop on every host."""
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    if _stale(LOADERS, LOADER_SRCS + [ROOT / "include" / "sparsewave_benchmark_utils.h", Path(__file__)]):
+        cmd = [shutil.which("g++") or "g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+               "-ffp-contract=off", *map(str, LOADER_SRCS), "-o", str(LOADERS)]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+    return LOADERS
 
 
 if __name__ == "__main__":
