@@ -323,6 +323,26 @@ def run_ours(args):
         total_ms = timed(step, args.steps)
         launches1 = ctx.kernel_launches
         barrier()
+        # The reference's own convention (benchmark/benchmark_utils.py:520-521): 10 warm-up dispatches, 50
+        # timed ones, each with its own event pair; median / min / p95 of those (max over ranks per dispatch).
+        per_dispatch = []
+        for i in range(60):
+            if flush is not None:
+                flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            if i >= 10:
+                per_dispatch.append((e0, e1))
+        torch.cuda.synchronize()
+        times = torch.tensor([a.elapsed_time(b) for a, b in per_dispatch], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        times = sorted(times.tolist())
+        dispatch_stats = {"warmup": 10, "dispatches": 50, "median_ms": times[len(times) // 2], "min_ms": times[0],
+                          "p95_ms": times[min(len(times) - 1, int(round(0.95 * (len(times) - 1))))]}
+        barrier()
         # Keep the same steps running for about 0.3 s so that the sampler sees the clocks under this
         # load.  The step count comes from the rank-reduced time, so every rank runs the same number
         # of steps (they contain a collective when N > 1).
@@ -392,7 +412,7 @@ def run_ours(args):
                    "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
                    "launch": "CUDA graph of one step, replayed" if graph is not None else "host launch per step"},
         "gflops": gflops, "frac_of_hbm_peak": gbs / (peak * world), "gpu_launches": int(gpu_launches),
-        "clocks": clocks.summary(), "e2e": e2e,
+        "clocks": clocks.summary(), "e2e": e2e, "dispatch_stats": dispatch_stats,
     }
     if world == 1:
         line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,

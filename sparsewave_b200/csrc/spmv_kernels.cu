@@ -251,6 +251,25 @@ __device__ __forceinline__ int block_first_rows(const int32_t *__restrict__ row_
   return v;
 }
 
+// y[key] += value for every lane with key >= 0, all 32 lanes calling.  Lanes with equal keys must be
+// adjacent (keys non-decreasing over the lanes, the negative ones last): each run of equal keys is added
+// up with a segmented shuffle scan and its last lane issues the one atomicAdd of the run.
+__device__ __forceinline__ void warp_add_runs(float *__restrict__ y, int key, float value, int lane) {
+  const int below = __shfl_up_sync(FULL, key, 1);
+  const bool head = lane == 0 || below != key;
+  const unsigned hmask = __ballot_sync(FULL, head);
+  const unsigned le = (lane == 31) ? FULL : ((1u << (lane + 1)) - 1u);
+  const int dist = lane - (31 - __clz(hmask & le));
+  float S = value;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float t = __shfl_up_sync(FULL, S, off);
+    if (off <= dist) S = add(S, t);
+  }
+  const bool last = lane == 31 || ((hmask >> (lane + 1)) & 1u);
+  if (key >= 0 && last) atomicAdd(y + key, S);
+}
+
 template <bool SEGMENTED, bool TRACE, bool COOP>
 __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64_t chunk,
                                                 const int32_t *__restrict__ row_ptr,
@@ -274,12 +293,42 @@ __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64
     if (ce <= cb) ce = nnz;  // the last worker of the block is past the end: the block reaches nnz
     if (w0 * chunk >= nnz) return;  // whole block inactive (only the clamped grid of an empty matrix)
     row = block_first_rows(row_ptr, rows, cb, ce, chunk, marks, warp_tot);
-    if (begin >= end) return;
+    if constexpr (!SEGMENTED) {
+      // Atomic schedule on whole warps: at step j the lanes hold positions `chunk` apart, so their rows
+      // are non-decreasing and equal rows sit in adjacent lanes.  The products of such a run are added
+      // by warp_add_runs and the run's last lane issues one atomicAdd for all of them: the same additions
+      // into y as one atomicAdd per position, far fewer of them on the same address.
+      const int lane = threadIdx.x & 31;
+      int64_t nxt = begin < end ? row_ptr[row + 1] : 0;
+      for (int64_t j = 0; j < chunk; ++j) {
+        const int64_t p = begin + j;
+        const bool valid = p < end;
+        if (__ballot_sync(FULL, valid) == 0) break;
+        float prod = 0.0f;
+        if (valid) {
+          while (nxt <= p) {
+            ++row;
+            nxt = row_ptr[row + 1];
+          }
+          prod = mul(ld_stream(val + p), __ldg(x + ld_stream(col + p)));
+          if (TRACE) {
+            trace.row_of_position[p] = (int32_t)row;
+            trace.worker_of_position[p] = (int32_t)worker;
+            trace.segment_end[p] = 1;
+          }
+        }
+        warp_add_runs(y, valid ? (int)row : -1, prod, lane);
+      }
+      return;
+    }
   } else {
     if (begin >= end) return;
     row = row_at_position(row_ptr, rows + 1, begin);
   }
-  int64_t next = row_ptr[row + 1];
+  // From here: the segmented schedule, and the atomic one on blocks that are not made of whole warps.
+  // With whole warps the threads past the last position stay for the warp-wide flush at the end.
+  const bool live = begin < end;
+  int64_t next = live ? row_ptr[row + 1] : 0;
   float acc = 0.0f;
   int64_t acc_row = row;
   for (int64_t p = begin; p < end; ++p) {
@@ -307,8 +356,11 @@ __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64
     }
   }
   if (SEGMENTED) {
-    atomicAdd(y + acc_row, acc);
-    if (TRACE) trace.segment_end[end - 1] = 1;
+    // Last open segment of every worker.  On whole warps the workers' last rows are non-decreasing over
+    // the lanes, so workers that end inside the same long row share one atomicAdd.
+    if (COOP) warp_add_runs(y, live ? (int)acc_row : -1, acc, threadIdx.x & 31);
+    else atomicAdd(y + acc_row, acc);
+    if (TRACE && live) trace.segment_end[end - 1] = 1;
   }
 }
 
