@@ -251,9 +251,9 @@ __device__ __forceinline__ int block_first_rows(const int32_t *__restrict__ row_
   return v;
 }
 
-// y[key] += value for every lane with key >= 0, all 32 lanes calling.  Lanes with equal keys must be
-// adjacent (keys non-decreasing over the lanes, the negative ones last): each run of equal keys is added
-// up with a segmented shuffle scan and its last lane issues the one atomicAdd of the run.
+// y[key] += value for every lane with key >= 0, all 32 lanes calling.  Each run of adjacent lanes with the
+// same key is added up with a segmented shuffle scan and its last lane issues the one atomicAdd of the
+// run (keys in any order are handled; sorted keys give the longest runs).
 __device__ __forceinline__ void warp_add_runs(float *__restrict__ y, int key, float value, int lane) {
   const int below = __shfl_up_sync(FULL, key, 1);
   const bool head = lane == 0 || below != key;
@@ -370,11 +370,21 @@ __global__ void spmv_thread_per_position_kernel(int64_t rows, int64_t nnz, int64
 // + threadIdx adds val * x[col] to y[row] with one atomicAdd; duplicate
 // coordinates simply add twice.
 // ---------------------------------------------------------------------------
+template <bool WHOLE_WARPS>
 __global__ void coo_spmv_thread_per_nonzero_kernel(int64_t nnz, const int32_t *__restrict__ row,
                                                    const int32_t *__restrict__ col,
                                                    const float *__restrict__ val,
                                                    const float *__restrict__ x, float *__restrict__ y) {
   const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (WHOLE_WARPS) {
+    // Entries of one row that sit in adjacent lanes (row-sorted files) share one atomicAdd.
+    if (p - (threadIdx.x & 31) >= nnz) return;  // whole warp past the end
+    const bool valid = p < nnz;
+    const int r = valid ? ld_stream(row + p) : -1;
+    const float prod = valid ? mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))) : 0.0f;
+    warp_add_runs(y, r, prod, threadIdx.x & 31);
+    return;
+  }
   if (p >= nnz) return;
   atomicAdd(y + ld_stream(row + p), mul(ld_stream(val + p), __ldg(x + ld_stream(col + p))));
 }
@@ -625,7 +635,10 @@ cudaError_t launch_coo_spmv_thread_per_nonzero(int64_t rows, int64_t nnz, const 
                                                cudaStream_t s, int64_t *launches) {
   cudaError_t e = launch_fill_zero(y, rows, block, s, launches);
   if (e != cudaSuccess) return e;
-  coo_spmv_thread_per_nonzero_kernel<<<grid_of(ceil_div(nnz, block)), block, 0, s>>>(nnz, row, col, val, x, y);
+  if (block % 32 == 0)
+    coo_spmv_thread_per_nonzero_kernel<true><<<grid_of(ceil_div(nnz, block)), block, 0, s>>>(nnz, row, col, val, x, y);
+  else
+    coo_spmv_thread_per_nonzero_kernel<false><<<grid_of(ceil_div(nnz, block)), block, 0, s>>>(nnz, row, col, val, x, y);
   ++*launches;
   return cudaGetLastError();
 }
