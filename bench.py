@@ -71,6 +71,9 @@ def parse_args():
                    help="N > 1: run the locally-owned columns of the shard while the all-gather is in flight")
     p.add_argument("--torch-collective", action="store_true",
                    help="N > 1: all-gather through torch.distributed instead of the library's communicator")
+    p.add_argument("--p2p-allgather", action="store_true",
+                   help="N > 1: all-gather with the library's own peer-store kernel (CUDA IPC window over NVLink) "
+                        "instead of ncclAllGather on the library's communicator")
     p.add_argument("--replicated", action="store_true",
                    help="N > 1: dense operand already replicated, no all-gather in the step")
     return p.parse_args()
@@ -208,6 +211,7 @@ def run_ours(args):
     opts = make_options(options)  # parsed once; the steps pass the option block
     wl = build_workload(args.workload, device, args.rows)
     kind, a, dense = wl["kind"], wl["a"], wl["dense"]
+    gather_kind = "library NCCL communicator"
 
     # ---- this rank's share --------------------------------------------------------------
     if world > 1 and kind == "bsr":
@@ -223,6 +227,22 @@ def run_ours(args):
     elif world > 1:
         shard = sharding.shard_csr(a.row_ptr, a.col_idx, a.values, a.cols, rank, world)
         overlap = args.overlap and not args.replicated and not args.torch_collective
+        if args.p2p_allgather and not (args.torch_collective or args.replicated or overlap):
+            nbytes = sharding.window_bytes(a.cols, world, tuple(dense.shape[1:]), dense.element_size())
+            if nbytes % 16 == 0:
+                try:
+                    ctx.window_create(nbytes)
+                    made = 1
+                except Exception as exc:  # noqa: BLE001  (no CUDA IPC between these processes: NCCL stays)
+                    print(f"bench: peer window unavailable, using ncclAllGather: {exc}", file=sys.stderr)
+                    made = 0
+                agreed = torch.tensor([made], dtype=torch.int32, device=device)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # every rank uses the window, or none does
+                torch.cuda.synchronize()
+                if int(agreed.item()) == 1:
+                    gather_kind = "peer-store kernel over NVLink into an IPC window"
+                elif made:
+                    ctx.window_destroy()
         op = sharding.OverlappedShardedOperator(ctx, shard, opts) if overlap else \
             sharding.ShardedOperator(ctx, shard, opts)
         lo, hi = sharding.owned_dense_range(a.cols, world, rank)
@@ -407,7 +427,7 @@ def run_ours(args):
                    "bytes_algorithmic": wl["bytes"], "flops": wl["flops"],
                    "dense_operand": "replicated" if (world == 1 or args.replicated) else
                    ("all-gathered each step (torch.distributed)" if args.torch_collective
-                    else "all-gathered each step (library NCCL communicator)" +
+                    else f"all-gathered each step ({gather_kind})" +
                     (", overlapped with the locally-owned columns" if args.overlap else "")),
                    "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
                    "launch": "CUDA graph of one step, replayed" if graph is not None else "host launch per step"},

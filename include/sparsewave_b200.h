@@ -403,6 +403,25 @@ SWB_API int swb_comm_allgather(swb_context *ctx, const void *send, void *recv,
                                int64_t bytes_per_rank, swb_stream stream);
 SWB_API void swb_comm_destroy(swb_context *ctx);
 
+/* The same exchange as one kernel of peer stores over NVLink instead of
+ * ncclAllGather.  swb_comm_window_create (collective over the communicator's
+ * ranks, which must be processes of one node) allocates a window of n_ranks *
+ * bytes_per_rank bytes on every rank, maps the windows of the other ranks with
+ * CUDA IPC and returns this rank's window; bytes_per_rank must be a multiple
+ * of 16.  swb_comm_window_allgather queues one kernel on `stream` that stores
+ * the bytes_per_rank bytes at `send` (16-byte aligned device memory) into
+ * every rank's window at offset rank * bytes_per_rank; work queued behind it
+ * on the same stream finds the whole window filled.  A window must not be read
+ * by other streams while a later all-gather may overwrite it.  The kernel's
+ * waits on the other ranks are bounded: if one gives up (a rank that never
+ * launches its step), swb_device_status reports 3 or 4 and the window content
+ * is not valid.  One window per context; capturable in a CUDA graph. */
+SWB_API int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank,
+                                   void **window);
+SWB_API int swb_comm_window_allgather(swb_context *ctx, const void *send,
+                                      swb_stream stream);
+SWB_API void swb_comm_window_destroy(swb_context *ctx);
+
 /* ---- multi-GPU row sharding --------------------------------------------- */
 /* nnz-balanced contiguous row shards: boundaries[k] = the first row r with
  * row_ptr[r] >= k * nnz / n_shards (exact integer arithmetic), boundaries[0]

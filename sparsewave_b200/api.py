@@ -84,6 +84,7 @@ class Context:
 
     def close(self) -> None:
         if self._ctx:
+            self.window = None
             self._lib.swb_destroy(self._ctx)
             self._ctx = C.c_void_p()
 
@@ -153,6 +154,37 @@ class Context:
             raise ValueError("recv must hold world x send bytes")
         self._check(self._lib.swb_comm_allgather(self._ctx, send.data_ptr(), recv.data_ptr(), nbytes, self._stream()))
         return recv
+
+    # -- all-gather as one kernel of peer stores (processes of one node) ---------------
+    def window_create(self, bytes_per_rank: int) -> torch.Tensor:
+        """Collective over the communicator's ranks: allocates this rank's window of comm_world *
+        bytes_per_rank bytes, maps the other ranks' windows and returns a uint8 tensor over the local one."""
+        ptr = C.c_void_p()
+        self._check(self._lib.swb_comm_window_create(self._ctx, int(bytes_per_rank), C.byref(ptr)))
+        self.window_bytes_per_rank = int(bytes_per_rank)
+
+        class _Window:  # device memory owned by the library, exposed through the CUDA array interface
+            __cuda_array_interface__ = {"shape": (int(bytes_per_rank) * self.comm_world,), "typestr": "|u1",
+                                        "data": (int(ptr.value), False), "version": 3, "strides": None}
+
+        self.window = torch.as_tensor(_Window(), device=torch.device("cuda", self.device))
+        return self.window
+
+    def window_allgather(self, send: torch.Tensor) -> torch.Tensor:
+        """Stores `send` (window_bytes_per_rank bytes, contiguous, 16-byte aligned) into every rank's window
+        at this rank's offset, on the current stream; returns the local window."""
+        if getattr(self, "window", None) is None:
+            raise ValueError("the context has no window (window_create)")
+        if not (send.is_cuda and send.is_contiguous()) or send.numel() * send.element_size() != self.window_bytes_per_rank:
+            raise ValueError("send must be a contiguous CUDA tensor of window_bytes_per_rank bytes")
+        self._check(self._lib.swb_comm_window_allgather(self._ctx, send.data_ptr(), self._stream()))
+        return self.window
+
+    def window_destroy(self) -> None:
+        """Collective: unmaps the peers' windows and frees this rank's."""
+        if getattr(self, "window", None) is not None:
+            self.window = None
+            self._lib.swb_comm_window_destroy(self._ctx)
 
     def validate(self, options) -> None:
         self._check(self._lib.swb_options_validate(self._ctx, C.byref(self._opts(options))))

@@ -29,6 +29,7 @@ struct swb_context {
   cudaEvent_t panel_done[8] = {};
   int *status_flag = nullptr;  // device int for kernels with bounded waits
   void *comm = nullptr;        // NCCL communicator of the multi-GPU path (swb_comm.cu)
+  void *peer_window = nullptr; // peer-store all-gather window (swb_peer_window.cu)
   int comm_ranks = 1, comm_rank = 0;
 };
 
@@ -63,6 +64,15 @@ void set_context_comm(swb_context *ctx, void *comm, int n_ranks, int rank) {
   ctx->comm_ranks = n_ranks;
   ctx->comm_rank = rank;
 }
+bool context_comm_shape(const swb_context *ctx, int *n_ranks, int *rank) {
+  *n_ranks = ctx->comm_ranks;
+  *rank = ctx->comm_rank;
+  return ctx->comm != nullptr;
+}
+void *context_peer_window(const swb_context *ctx) { return ctx->peer_window; }
+void set_context_peer_window(swb_context *ctx, void *window) { ctx->peer_window = window; }
+int *context_status_flag(const swb_context *ctx) { return ctx->status_flag; }
+void count_launch(swb_context *ctx) { ++ctx->launches; }
 }  // namespace swb
 
 namespace {
@@ -226,6 +236,7 @@ int swb_device_status(swb_context *ctx, swb_stream stream, int32_t *status) {
 void swb_destroy(swb_context *ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
+  swb_comm_window_destroy(ctx);
   swb_comm_destroy(ctx);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->status_flag) cudaFree(ctx->status_flag);

@@ -114,6 +114,11 @@ void set_context_error(swb_context *ctx, const char *message);
 int context_device(const swb_context *ctx);
 void *context_comm(const swb_context *ctx);
 void set_context_comm(swb_context *ctx, void *comm, int n_ranks, int rank);
+bool context_comm_shape(const swb_context *ctx, int *n_ranks, int *rank);  // false without a communicator
+void *context_peer_window(const swb_context *ctx);
+void set_context_peer_window(swb_context *ctx, void *window);
+int *context_status_flag(const swb_context *ctx);
+void count_launch(swb_context *ctx);
 
 // Stores the diagnostic that swb_last_error(NULL) returns on this thread.
 void set_thread_error(const char *message);

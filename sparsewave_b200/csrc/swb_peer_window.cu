@@ -1,0 +1,244 @@
+// All-gather of the dense operand as one kernel of peer stores over NVLink.
+//
+// Every rank owns a window: a device allocation of [4 KiB header][n_ranks * bytes_per_rank data] exported to
+// the other ranks of the node with CUDA IPC (the handles travel through the context's NCCL communicator at
+// set-up).  A step is one kernel per rank that
+//   1. tells every peer "I no longer read my window" (ready flag, epoch-numbered; stream order guarantees
+//      that the kernel that consumed the previous epoch has finished),
+//   2. waits until every peer has said the same, so no window is overwritten while it is read,
+//   3. stores its own chunk into every rank's window (plain 16-byte peer stores; its own window included),
+//   4. once all its CTAs have fenced their stores, raises its done flag in every window,
+//   5. waits until every peer's done flag is up, so that the kernel after it finds the window complete.
+// All waits poll flags in this GPU's own memory that only the other ranks write, are bounded, and give up
+// by setting the context's status word (swb_device_status) instead of spinning on; CTAs of one grid never
+// wait for one another, so the grid needs no co-residency.
+// Plain loads and stores only.  Not a reference feature.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/sparsewave_b200.h"
+#include "swb_kernels.h"
+
+namespace swb {
+namespace {
+
+constexpr int kMaxRanks = 16;
+constexpr int64_t kHeaderBytes = 4096;
+constexpr int kReadyOff = 0, kDoneOff = 256, kEpochOff = 512, kArrivedOff = 516;
+constexpr unsigned kPollLimit = 1u << 24;  // polls of a flag in local memory, 100 ns apart (a few seconds), before giving up
+constexpr int kSlices = 32;                // CTAs per destination rank
+
+struct PeerWindow {
+  int ranks = 1, rank = 0;
+  int64_t bytes_per_rank = 0;
+  char *local = nullptr;
+  char *peer[kMaxRanks] = {};
+  char **d_peer = nullptr;
+};
+
+// true when flag[i] has reached `epoch` (epochs compared modulo 2^32) before the poll limit
+__device__ bool wait_flag(const volatile unsigned *flag, unsigned epoch) {
+  for (unsigned n = 0; n < kPollLimit; ++n) {
+    if ((int)(*flag - epoch) >= 0) return true;
+    __nanosleep(100);
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restrict__ send, int64_t n16,
+                                                             char *const *__restrict__ peer, int rank, int ranks,
+                                                             int64_t bytes_per_rank, int *status) {
+  char *local = peer[rank];
+  __shared__ unsigned s_epoch;
+  __shared__ int s_failed;
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile unsigned *>(local + kEpochOff) + 1u;
+    s_failed = 0;
+    s_last = 0;
+  }
+  __syncthreads();
+  const unsigned epoch = s_epoch;
+
+  // 1. ready flags out (one CTA is enough), 2. ready flags in (every CTA looks for itself)
+  if (blockIdx.x == 0 && threadIdx.x < ranks)
+    reinterpret_cast<volatile unsigned *>(peer[threadIdx.x] + kReadyOff)[rank] = epoch;
+  if (threadIdx.x < ranks && threadIdx.x != rank &&
+      !wait_flag(reinterpret_cast<volatile unsigned *>(local + kReadyOff) + threadIdx.x, epoch))
+    s_failed = 1;
+  __syncthreads();
+
+  // 3. this rank's chunk into the window of rank `dst`; the CTAs of one destination interleave by slice.
+  // After a failed wait the stores still go out (they stay inside the windows) so that the counters below
+  // remain consistent; the status word tells the host that the result is not to be trusted.
+  const int dst = blockIdx.x % ranks, slice = blockIdx.x / ranks, slices = gridDim.x / ranks;
+  int4 *out = reinterpret_cast<int4 *>(peer[dst] + kHeaderBytes + (int64_t)rank * bytes_per_rank);
+  const int64_t stride = (int64_t)slices * blockDim.x;
+  int64_t i = (int64_t)slice * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    const int4 a = __ldg(send + i), b = __ldg(send + i + stride), c = __ldg(send + i + 2 * stride),
+               d = __ldg(send + i + 3 * stride);
+    out[i] = a; out[i + stride] = b; out[i + 2 * stride] = c; out[i + 3 * stride] = d;
+  }
+  for (; i < n16; i += stride) out[i] = __ldg(send + i);
+
+  // 4. the CTA's stores are ordered before its count; the CTA that counts last speaks for the rank
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned before = atomicAdd(reinterpret_cast<unsigned *>(local + kArrivedOff), 1u);
+    s_last = before == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_failed && threadIdx.x == 0) atomicExch(status, 3);
+  if (!s_last) return;
+
+  __threadfence_system();
+  if (threadIdx.x < ranks) reinterpret_cast<volatile unsigned *>(peer[threadIdx.x] + kDoneOff)[rank] = epoch;
+  // 5. every peer's chunk has landed here
+  if (threadIdx.x < ranks && threadIdx.x != rank &&
+      !wait_flag(reinterpret_cast<volatile unsigned *>(local + kDoneOff) + threadIdx.x, epoch))
+    atomicExch(status, 4);
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile unsigned *>(local + kArrivedOff) = 0u;
+    *reinterpret_cast<volatile unsigned *>(local + kEpochOff) = epoch;
+  }
+}
+
+int window_fail(swb_context *ctx, int status, const char *what, const char *detail) {
+  char buf[512];
+  snprintf(buf, sizeof buf, "%s: %s", what, detail);
+  set_context_error(ctx, buf);
+  return status;
+}
+
+void release(PeerWindow *w) {
+  if (!w) return;
+  for (int k = 0; k < w->ranks; ++k)
+    if (k != w->rank && w->peer[k]) cudaIpcCloseMemHandle(w->peer[k]);
+  if (w->d_peer) cudaFree(w->d_peer);
+  if (w->local) cudaFree(w->local);
+  delete w;
+}
+
+}  // namespace
+}  // namespace swb
+
+extern "C" {
+
+int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **window) {
+  using namespace swb;
+  if (!ctx) {
+    set_thread_error("context is NULL");
+    return SWB_ERR_INVALID_ARGUMENT;
+  }
+  if (!window) return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window", "window is NULL");
+  *window = nullptr;
+  int ranks = 1, rank = 0;
+  if (!context_comm_shape(ctx, &ranks, &rank))
+    return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window", "the context has no communicator (swb_comm_init)");
+  if (ranks > kMaxRanks) return window_fail(ctx, SWB_ERR_UNSUPPORTED, "window", "more than 16 ranks");
+  if (bytes_per_rank <= 0 || bytes_per_rank % 16 != 0)
+    return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window", "bytes_per_rank must be a positive multiple of 16");
+  if (context_peer_window(ctx)) return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window", "the context already has a window");
+  cudaError_t e = cudaSetDevice(context_device(ctx));
+  if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "cudaSetDevice", cudaGetErrorString(e));
+
+  PeerWindow *w = new PeerWindow();
+  w->ranks = ranks; w->rank = rank; w->bytes_per_rank = bytes_per_rank;
+  const size_t total = (size_t)kHeaderBytes + (size_t)ranks * (size_t)bytes_per_rank;
+  cudaIpcMemHandle_t mine;
+  cudaIpcMemHandle_t *d_handles = nullptr;
+  cudaIpcMemHandle_t all[kMaxRanks];
+  e = cudaMalloc(&w->local, total);
+  if (e == cudaSuccess) e = cudaMemset(w->local, 0, (size_t)kHeaderBytes);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine, w->local);
+  if (e == cudaSuccess) e = cudaMalloc(&d_handles, sizeof(mine) * (size_t)(ranks + 1));
+  if (e == cudaSuccess) e = cudaMemcpy(d_handles + ranks, &mine, sizeof mine, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(d_handles);
+    release(w);
+    return window_fail(ctx, SWB_ERR_CUDA, "window allocation", cudaGetErrorString(e));
+  }
+  // The handles travel through the context's communicator; the header is zero on every rank before any
+  // rank can reach a peer (the exchange is a collective that follows the memset).
+  int st = swb_comm_allgather(ctx, d_handles + ranks, d_handles, (int64_t)sizeof mine, nullptr);
+  if (st == SWB_OK) {
+    e = cudaStreamSynchronize(nullptr);
+    if (e == cudaSuccess) e = cudaMemcpy(all, d_handles, sizeof(mine) * (size_t)ranks, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) st = window_fail(ctx, SWB_ERR_CUDA, "window handle exchange", cudaGetErrorString(e));
+  }
+  cudaFree(d_handles);
+  for (int k = 0; st == SWB_OK && k < ranks; ++k) {
+    if (k == rank) {
+      w->peer[k] = w->local;
+      continue;
+    }
+    void *p = nullptr;
+    e = cudaIpcOpenMemHandle(&p, all[k], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) st = window_fail(ctx, SWB_ERR_CUDA, "cudaIpcOpenMemHandle", cudaGetErrorString(e));
+    w->peer[k] = static_cast<char *>(p);
+  }
+  if (st == SWB_OK) {
+    e = cudaMalloc(&w->d_peer, sizeof(char *) * kMaxRanks);
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_peer, w->peer, sizeof(char *) * kMaxRanks, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) st = window_fail(ctx, SWB_ERR_CUDA, "window peer table", cudaGetErrorString(e));
+  }
+  if (st != SWB_OK) {
+    release(w);
+    return st;
+  }
+  set_context_peer_window(ctx, w);
+  *window = w->local + kHeaderBytes;
+  return SWB_OK;
+}
+
+int swb_comm_window_allgather(swb_context *ctx, const void *send, swb_stream stream) {
+  using namespace swb;
+  if (!ctx) {
+    set_thread_error("context is NULL");
+    return SWB_ERR_INVALID_ARGUMENT;
+  }
+  PeerWindow *w = static_cast<PeerWindow *>(context_peer_window(ctx));
+  if (!w) return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window all-gather", "the context has no window (swb_comm_window_create)");
+  if (!send || (reinterpret_cast<uintptr_t>(send) & 15u))
+    return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window all-gather", "send must be a 16-byte aligned device pointer");
+  cudaError_t e = cudaSetDevice(context_device(ctx));
+  if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "cudaSetDevice", cudaGetErrorString(e));
+  peer_allgather_kernel<<<(unsigned)(w->ranks * kSlices), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int4 *>(send), w->bytes_per_rank / 16, w->d_peer, w->rank, w->ranks, w->bytes_per_rank,
+      context_status_flag(ctx));
+  count_launch(ctx);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "window all-gather launch", cudaGetErrorString(e));
+  return SWB_OK;
+}
+
+void swb_comm_window_destroy(swb_context *ctx) {
+  using namespace swb;
+  if (!ctx) return;
+  PeerWindow *w = static_cast<PeerWindow *>(context_peer_window(ctx));
+  if (!w) return;
+  cudaSetDevice(context_device(ctx));
+  cudaDeviceSynchronize();
+  // Unmap the peers' windows, then make sure every rank has done so before any window is freed (memory
+  // must not be freed while another process still maps it): a 4-byte all-gather inside the header.
+  for (int k = 0; k < w->ranks; ++k)
+    if (k != w->rank && w->peer[k]) {
+      cudaIpcCloseMemHandle(w->peer[k]);
+      w->peer[k] = nullptr;
+    }
+  int ranks = 1, rank = 0;
+  if (w->ranks > 1 && context_comm_shape(ctx, &ranks, &rank) &&
+      swb_comm_allgather(ctx, w->local + 1024, w->local + 2048, 4, nullptr) == SWB_OK)
+    cudaStreamSynchronize(nullptr);
+  release(w);
+  set_context_peer_window(ctx, nullptr);
+}
+
+}  // extern "C"

@@ -130,6 +130,17 @@ def allgather_dense(owned: torch.Tensor, n_rows: int, out: Optional[torch.Tensor
     world = ctx.comm_world if native else (dist.get_world_size(group) if dist.is_initialized() else 1)
     chunk = dense_chunk(n_rows, world)
     tail = tuple(owned.shape[1:])
+    window = getattr(ctx, "window", None) if native else None
+    if window is not None:
+        # the library's own all-gather kernel (peer stores over NVLink) into the library-owned window
+        if chunk * int(np.prod(tail, dtype=np.int64)) * owned.element_size() != ctx.window_bytes_per_rank:
+            raise ValueError("the context's window was created for another operand size")
+        send = owned
+        if owned.shape[0] != chunk:
+            send = torch.zeros((chunk,) + tail, dtype=owned.dtype, device=owned.device)
+            send[:owned.shape[0]].copy_(owned)
+        full = ctx.window_allgather(send.contiguous()).view(owned.dtype).view((chunk * world,) + tail)
+        return full[:n_rows]
     if out is None:
         out = torch.empty((chunk * world,) + tail, dtype=owned.dtype, device=owned.device)
     if world == 1:
@@ -212,9 +223,16 @@ class OverlappedShardedOperator:
                                                                              out, rows=p.rows))
 
 
+def window_bytes(n_rows: int, world: int, tail=(), element_size: int = 4) -> int:
+    """Bytes per rank of the window that gathers an operand of n_rows rows (`Context.window_create`)."""
+    return dense_chunk(n_rows, world) * int(np.prod(tail, dtype=np.int64)) * element_size
+
+
 class ShardedOperator:
     """A row shard bound to a library context: gathers the dense operand, then
-    runs the local kernel on this rank's rows."""
+    runs the local kernel on this rank's rows.  The gather is the library's peer-store kernel when the
+    context has a window (`Context.window_create`), its NCCL all-gather when it has a communicator,
+    torch.distributed's otherwise."""
 
     def __init__(self, ctx: api.Context, shard: CsrShard, options, group=None):
         self.ctx, self.shard, self.options, self.group = ctx, shard, options, group
@@ -222,6 +240,8 @@ class ShardedOperator:
 
     def _gather(self, owned: torch.Tensor, n_rows: int) -> torch.Tensor:
         world = self.shard.world
+        if getattr(self.ctx, "window", None) is not None:
+            return allgather_dense(owned, n_rows, None, self.group, self.ctx)
         chunk = dense_chunk(n_rows, world)
         shape = (chunk * world,) + tuple(owned.shape[1:])
         if self._full is None or tuple(self._full.shape) != shape or self._full.dtype != owned.dtype:

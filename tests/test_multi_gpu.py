@@ -40,6 +40,23 @@ def _rank_main(rank, world, port):
         assert np.all(np.abs(y2 - y) <= 1e-5 * oracle.csr_abs_bound(rp, ci, v, xh)[rows] + 1e-30)
         bound = oracle.csr_abs_bound(rp, ci, v, xh)[rows]
         assert np.all(np.abs(y - oracle.csr_spmv(rp, ci, v, xh)[rows]) <= 1e-5 * bound + 1e-30)
+        # the library's own all-gather: one kernel of peer stores into an IPC window, several steps in a row
+        # with a different x each (a step must not overwrite a window that a peer still reads)
+        ctx.window_create(sharding.window_bytes(a.cols, world))
+        for step in range(4):
+            xs = x * float(step + 1)
+            y4 = op.spmv(xs[lo:hi].contiguous()).cpu().numpy()
+            want = oracle.csr_spmv(rp, ci, v, xh * np.float32(step + 1))[rows]
+            assert np.all(np.abs(y4 - want) <= 1e-5 * (step + 1) * bound + 1e-30)
+            assert torch.equal(ctx.window.view(torch.float32)[:a.cols], xs)
+        assert ctx.device_status() == 0
+        ctx.window_destroy()
+        ctx.window_create(sharding.window_bytes(a.cols, world, (8,)))
+        opw = sharding.ShardedOperator(ctx, shard, "spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128")
+        Cw = opw.spmm(B[lo:hi].contiguous()).cpu().numpy()
+        assert np.all(np.abs(Cw - oracle.csr_spmm(rp, ci, v, Bh)[rows]) <= 1e-5 * oracle.csr_abs_bound(rp, ci, v, Bh)[rows] + 1e-30)
+        assert ctx.device_status() == 0
+        ctx.window_destroy()
         op = sharding.ShardedOperator(ctx, shard, "spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128")
         C = op.spmm(B[lo:hi].contiguous()).cpu().numpy()
         bound = oracle.csr_abs_bound(rp, ci, v, Bh)[rows]
