@@ -370,6 +370,9 @@ def run_ours(args):
         for _ in range(soak_steps):
             step()
         barrier()
+    device_status = ctx.device_status()  # non-zero: a bounded device-side wait gave up, the numbers are void
+    if device_status != 0:
+        print(f"bench: rank {rank}: device status {device_status}: a bounded wait gave up", file=sys.stderr)
     gpu_launches = launches1 - launches0 if graph is None else launches_per_step * args.steps
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
@@ -432,7 +435,7 @@ def run_ours(args):
                    "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
                    "launch": "CUDA graph of one step, replayed" if graph is not None else "host launch per step"},
         "gflops": gflops, "frac_of_hbm_peak": gbs / (peak * world), "gpu_launches": int(gpu_launches),
-        "clocks": clocks.summary(), "e2e": e2e, "dispatch_stats": dispatch_stats,
+        "clocks": clocks.summary(), "e2e": e2e, "dispatch_stats": dispatch_stats, "device_status": device_status,
     }
     if world == 1:
         line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,

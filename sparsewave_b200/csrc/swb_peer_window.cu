@@ -29,7 +29,7 @@ constexpr int kMaxRanks = 16;
 constexpr int64_t kHeaderBytes = 4096;
 constexpr int kReadyOff = 0, kDoneOff = 256, kEpochOff = 512, kArrivedOff = 516;
 constexpr unsigned kPollLimit = 1u << 24;  // polls of a flag in local memory, 100 ns apart (a few seconds), before giving up
-constexpr int kSlices = 32;                // CTAs per destination rank
+constexpr int kGridTarget = 256;           // CTAs of a step, split evenly over the destination ranks
 
 struct PeerWindow {
   int ranks = 1, rank = 0;
@@ -210,7 +210,9 @@ int swb_comm_window_allgather(swb_context *ctx, const void *send, swb_stream str
     return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window all-gather", "send must be a 16-byte aligned device pointer");
   cudaError_t e = cudaSetDevice(context_device(ctx));
   if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "cudaSetDevice", cudaGetErrorString(e));
-  peer_allgather_kernel<<<(unsigned)(w->ranks * kSlices), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  // enough 16-byte loads in flight (16 KiB per CTA) to keep the NVLink egress busy whatever the rank count
+  const int slices = kGridTarget / w->ranks > 0 ? kGridTarget / w->ranks : 1;
+  peer_allgather_kernel<<<(unsigned)(w->ranks * slices), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const int4 *>(send), w->bytes_per_rank / 16, w->d_peer, w->rank, w->ranks, w->bytes_per_rank,
       context_status_flag(ctx));
   count_launch(ctx);
