@@ -1,0 +1,136 @@
+"""Model of the peer-store all-gather protocol (sparsewave_b200/csrc/swb_peer_window.cu) under random
+interleavings: R ranks, each running step after step one exchange kernel of G CTAs (of which only a few are
+resident at a time) followed by a consumer that reads its whole window.  Checks that every schedule
+finishes (no wait depends on a CTA that cannot run) and that a consumer never sees a chunk of another
+epoch (nothing is overwritten while it is read, nothing is read before it has landed)."""
+import random
+
+import pytest
+
+
+class Rank:
+    def __init__(self, ranks, slices):
+        self.ready = [0] * ranks
+        self.done = [0] * ranks
+        self.epoch = 0
+        self.arrived = 0
+        self.data = [[0] * slices for _ in range(ranks)]  # data[source rank][slice] = epoch of the content
+
+
+def exchange_cta(world, r, b, grid):
+    ranks = len(world)
+    me = world[r]
+    epoch = me.epoch + 1
+    yield
+    if b == 0:                                   # 1. ready flags out
+        for k in range(ranks):
+            world[k].ready[r] = epoch
+            yield
+    for k in range(ranks):                       # 2. ready flags in (not its own)
+        while k != r and me.ready[k] < epoch:
+            yield
+    dst, piece = b % ranks, b // ranks           # 3. this CTA's slice of the chunk into window dst
+    world[dst].data[r][piece] = epoch
+    yield
+    me.arrived += 1                              # 4. count the CTA; the last one speaks for the rank
+    if me.arrived != grid:
+        return
+    for k in range(ranks):
+        world[k].done[r] = epoch
+        yield
+    for k in range(ranks):                       # 5. every peer's chunk has landed
+        while k != r and me.done[k] < epoch:
+            yield
+    me.arrived = 0
+    me.epoch = epoch
+
+
+def consumer(world, r, step, errors):
+    for k in range(len(world)):
+        for piece, seen in enumerate(world[r].data[k]):
+            if seen != step:
+                errors.append((r, step, k, piece, seen))
+            yield
+
+
+def rank_program(world, r, steps, grid, resident, rng, errors):
+    """One rank's stream: kernels in order; inside an exchange kernel at most `resident` CTAs run at a
+    time, started in index order, each advanced in random order."""
+    for step in range(1, steps + 1):
+        waiting = [exchange_cta(world, r, b, grid) for b in range(grid)]
+        running = []
+        while waiting or running:
+            while waiting and len(running) < resident:
+                running.append(waiting.pop(0))
+            g = rng.choice(running)
+            try:
+                next(g)
+            except StopIteration:
+                running.remove(g)
+            yield
+        yield from consumer(world, r, step, errors)
+
+
+@pytest.mark.parametrize("ranks,slices,resident", [(2, 3, 1), (2, 4, 8), (4, 2, 2), (8, 1, 3), (3, 2, 1)])
+def test_every_schedule_finishes_and_windows_are_consistent(ranks, slices, resident):
+    grid = ranks * slices
+    for seed in range(30):
+        rng = random.Random(seed)
+        world = [Rank(ranks, slices) for _ in range(ranks)]
+        errors = []
+        programs = [rank_program(world, r, 5, grid, resident, rng, errors) for r in range(ranks)]
+        live = list(range(ranks))
+        ticks = 0
+        while live:
+            # uneven progress: one rank may run far ahead of the others within what the protocol allows
+            r = rng.choice(live) if rng.random() < 0.7 else live[0]
+            try:
+                next(programs[r])
+            except StopIteration:
+                live.remove(r)
+            ticks += 1
+            assert ticks < 2_000_000, "a schedule did not finish"
+        assert not errors, errors[:3]
+        assert all(w.epoch == 5 and w.arrived == 0 for w in world)
+
+
+def test_the_model_detects_a_missing_ready_wait():
+    """The same model without step 2 lets a fast rank overwrite a window that is still being read."""
+    def broken_cta(world, r, b, grid):
+        g = exchange_cta(world, r, b, grid)
+        me = world[r]
+        saved = me.ready
+        me.ready = [1 << 30] * len(world)  # every ready flag looks raised
+        try:
+            yield from g
+        finally:
+            me.ready = saved
+    found = False
+    for seed in range(40):
+        rng = random.Random(seed)
+        world = [Rank(2, 2) for _ in range(2)]
+        errors = []
+
+        def program(r):
+            for step in range(1, 6):
+                ctas = [broken_cta(world, r, b, 4) for b in range(4)]
+                while ctas:
+                    g = rng.choice(ctas)
+                    try:
+                        next(g)
+                    except StopIteration:
+                        ctas.remove(g)
+                    yield
+                yield from consumer(world, r, step, errors)
+        programs = [program(0), program(1)]
+        live = [0, 1]
+        for _ in range(100000):
+            if not live:
+                break
+            r = rng.choice(live)
+            try:
+                next(programs[r])
+            except StopIteration:
+                live.remove(r)
+        found = found or bool(errors)
+    assert found
