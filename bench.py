@@ -71,9 +71,9 @@ def parse_args():
                    help="N > 1: run the locally-owned columns of the shard while the all-gather is in flight")
     p.add_argument("--torch-collective", action="store_true",
                    help="N > 1: all-gather through torch.distributed instead of the library's communicator")
-    p.add_argument("--p2p-allgather", action="store_true",
-                   help="N > 1: all-gather with the library's own peer-store kernel (CUDA IPC window over NVLink) "
-                        "instead of ncclAllGather on the library's communicator")
+    p.add_argument("--nccl-allgather", action="store_true",
+                   help="N > 1: all-gather with ncclAllGather on the library's communicator instead of the "
+                        "library's own peer-store kernel (CUDA IPC windows over NVLink)")
     p.add_argument("--replicated", action="store_true",
                    help="N > 1: dense operand already replicated, no all-gather in the step")
     return p.parse_args()
@@ -227,22 +227,30 @@ def run_ours(args):
     elif world > 1:
         shard = sharding.shard_csr(a.row_ptr, a.col_idx, a.values, a.cols, rank, world)
         overlap = args.overlap and not args.replicated and not args.torch_collective
-        if args.p2p_allgather and not (args.torch_collective or args.replicated or overlap):
-            nbytes = sharding.window_bytes(a.cols, world, tuple(dense.shape[1:]), dense.element_size())
-            if nbytes % 16 == 0:
-                try:
-                    ctx.window_create(nbytes)
-                    made = 1
-                except Exception as exc:  # noqa: BLE001  (no CUDA IPC between these processes: NCCL stays)
-                    print(f"bench: peer window unavailable, using ncclAllGather: {exc}", file=sys.stderr)
-                    made = 0
-                agreed = torch.tensor([made], dtype=torch.int32, device=device)
-                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # every rank uses the window, or none does
+        nbytes = sharding.window_bytes(a.cols, world, tuple(dense.shape[1:]), dense.element_size())
+        if not (args.nccl_allgather or args.torch_collective or args.replicated or overlap) and nbytes % 16 == 0:
+            # The library's own exchange kernel.  Creation succeeds on every rank or on none; before it is
+            # used, two exchanges of a rank-coded pattern are checked on every rank, and one bad rank sends
+            # all of them back to ncclAllGather.
+            try:
+                ctx.window_create(nbytes)
+                probe = torch.full((nbytes // 4,), float(rank + 1), dtype=torch.float32, device=device)
+                for _ in range(2):
+                    ctx.window_allgather(probe)
+                torch.cuda.synchronize()
+                got = ctx.window.view(torch.float32).view(world, -1)
+                good = all(bool((got[k] == float(k + 1)).all()) for k in range(world)) and ctx.device_status() == 0
+                agreed = torch.tensor([int(good)], dtype=torch.int32, device=device)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
                 torch.cuda.synchronize()
                 if int(agreed.item()) == 1:
-                    gather_kind = "peer-store kernel over NVLink into an IPC window"
-                elif made:
+                    gather_kind = "peer-store kernel over NVLink into CUDA IPC windows"
+                else:
+                    print("bench: the peer-window self-check failed, using ncclAllGather", file=sys.stderr)
                     ctx.window_destroy()
+                del probe
+            except Exception as exc:  # noqa: BLE001  (no CUDA IPC between these processes: same on every rank)
+                print(f"bench: peer window unavailable, using ncclAllGather: {exc}", file=sys.stderr)
         op = sharding.OverlappedShardedOperator(ctx, shard, opts) if overlap else \
             sharding.ShardedOperator(ctx, shard, opts)
         lo, hi = sharding.owned_dense_range(a.cols, world, rank)

@@ -18,6 +18,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <string>
 
 #include "../../include/sparsewave_b200.h"
 #include "swb_kernels.h"
@@ -149,45 +150,73 @@ int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **wind
   cudaError_t e = cudaSetDevice(context_device(ctx));
   if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "cudaSetDevice", cudaGetErrorString(e));
 
+  // Creation succeeds on every rank or on none: a rank whose allocation or mapping fails still takes part
+  // in both exchanges (with an all-zero handle that no peer can open, then with its failure flag), so no
+  // rank is left waiting in a collective and no rank ends up with a window that a peer lacks.
   PeerWindow *w = new PeerWindow();
   w->ranks = ranks; w->rank = rank; w->bytes_per_rank = bytes_per_rank;
   const size_t total = (size_t)kHeaderBytes + (size_t)ranks * (size_t)bytes_per_rank;
-  cudaIpcMemHandle_t mine;
-  cudaIpcMemHandle_t *d_handles = nullptr;
-  cudaIpcMemHandle_t all[kMaxRanks];
+  struct Slot { cudaIpcMemHandle_t handle; int ok; int pad[3]; };  // one exchanged record, 80 bytes
+  Slot *d_slots = nullptr;  // [0, ranks): gathered, [ranks]: this rank's
+  Slot mine, all[kMaxRanks];
+  memset(&mine, 0, sizeof mine);
+  e = cudaMalloc(&d_slots, sizeof(Slot) * (size_t)(ranks + 1));
+  if (e != cudaSuccess) {
+    release(w);
+    return window_fail(ctx, SWB_ERR_CUDA, "window exchange buffer", cudaGetErrorString(e));
+  }
+  std::string why;
   e = cudaMalloc(&w->local, total);
   if (e == cudaSuccess) e = cudaMemset(w->local, 0, (size_t)kHeaderBytes);
-  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine, w->local);
-  if (e == cudaSuccess) e = cudaMalloc(&d_handles, sizeof(mine) * (size_t)(ranks + 1));
-  if (e == cudaSuccess) e = cudaMemcpy(d_handles + ranks, &mine, sizeof mine, cudaMemcpyHostToDevice);
-  if (e != cudaSuccess) {
-    cudaFree(d_handles);
-    release(w);
-    return window_fail(ctx, SWB_ERR_CUDA, "window allocation", cudaGetErrorString(e));
-  }
-  // The handles travel through the context's communicator; the header is zero on every rank before any
-  // rank can reach a peer (the exchange is a collective that follows the memset).
-  int st = swb_comm_allgather(ctx, d_handles + ranks, d_handles, (int64_t)sizeof mine, nullptr);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine.handle, w->local);
+  mine.ok = e == cudaSuccess;
+  if (!mine.ok) why = std::string("window allocation: ") + cudaGetErrorString(e);
+
+  auto exchange = [&]() -> int {  // this rank's slot to every rank; the header memset precedes it in stream order
+    cudaError_t ce = cudaMemcpy(d_slots + ranks, &mine, sizeof mine, cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "window exchange", cudaGetErrorString(ce));
+    int st = swb_comm_allgather(ctx, d_slots + ranks, d_slots, (int64_t)sizeof(Slot), nullptr);
+    if (st != SWB_OK) return st;
+    ce = cudaStreamSynchronize(nullptr);
+    if (ce == cudaSuccess) ce = cudaMemcpy(all, d_slots, sizeof(Slot) * (size_t)ranks, cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "window exchange", cudaGetErrorString(ce));
+    return SWB_OK;
+  };
+
+  int st = exchange();  // 1. handles
   if (st == SWB_OK) {
-    e = cudaStreamSynchronize(nullptr);
-    if (e == cudaSuccess) e = cudaMemcpy(all, d_handles, sizeof(mine) * (size_t)ranks, cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) st = window_fail(ctx, SWB_ERR_CUDA, "window handle exchange", cudaGetErrorString(e));
-  }
-  cudaFree(d_handles);
-  for (int k = 0; st == SWB_OK && k < ranks; ++k) {
-    if (k == rank) {
-      w->peer[k] = w->local;
-      continue;
+    for (int k = 0; k < ranks && mine.ok; ++k) {
+      if (k == rank) {
+        w->peer[k] = w->local;
+        continue;
+      }
+      void *p = nullptr;
+      e = all[k].ok ? cudaIpcOpenMemHandle(&p, all[k].handle, cudaIpcMemLazyEnablePeerAccess) : cudaErrorInvalidValue;
+      if (e != cudaSuccess) {
+        mine.ok = 0;
+        why = std::string("mapping the window of rank ") + std::to_string(k) + ": " + cudaGetErrorString(e);
+        cudaGetLastError();
+      }
+      w->peer[k] = static_cast<char *>(p);
     }
-    void *p = nullptr;
-    e = cudaIpcOpenMemHandle(&p, all[k], cudaIpcMemLazyEnablePeerAccess);
-    if (e != cudaSuccess) st = window_fail(ctx, SWB_ERR_CUDA, "cudaIpcOpenMemHandle", cudaGetErrorString(e));
-    w->peer[k] = static_cast<char *>(p);
+    if (mine.ok) {
+      e = cudaMalloc(&w->d_peer, sizeof(char *) * kMaxRanks);
+      if (e == cudaSuccess) e = cudaMemcpy(w->d_peer, w->peer, sizeof(char *) * kMaxRanks, cudaMemcpyHostToDevice);
+      if (e != cudaSuccess) {
+        mine.ok = 0;
+        why = std::string("window peer table: ") + cudaGetErrorString(e);
+      }
+    }
+    st = exchange();  // 2. who succeeded
   }
+  cudaFree(d_slots);
   if (st == SWB_OK) {
-    e = cudaMalloc(&w->d_peer, sizeof(char *) * kMaxRanks);
-    if (e == cudaSuccess) e = cudaMemcpy(w->d_peer, w->peer, sizeof(char *) * kMaxRanks, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) st = window_fail(ctx, SWB_ERR_CUDA, "window peer table", cudaGetErrorString(e));
+    for (int k = 0; k < ranks; ++k)
+      if (!all[k].ok) {
+        if (why.empty()) why = "rank " + std::to_string(k) + " could not create or map its window";
+        st = window_fail(ctx, SWB_ERR_CUDA, "window", why.c_str());
+        break;
+      }
   }
   if (st != SWB_OK) {
     release(w);
