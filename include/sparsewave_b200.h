@@ -368,7 +368,8 @@ typedef struct swb_launch_shape {
   int64_t logical_block;  /* threads per block                            */
   int64_t work_units;     /* rows, outputs, workers or waves               */
   int64_t kernels;        /* launches per call (2 for position mappings)   */
-  int64_t physical_grid;  /* CUDA blocks of the compute kernel             */
+  int64_t physical_grid;  /* CUDA blocks of the compute kernel (for 16-byte
+                             aligned operands)                             */
 } swb_launch_shape;
 SWB_API int swb_launch_shape_query(swb_context *ctx, const swb_options *opts,
                                    int64_t rows, int64_t nnz, int64_t n_rhs,

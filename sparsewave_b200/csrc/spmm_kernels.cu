@@ -459,6 +459,18 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
   return launch_tile<32>(a, block, tile, s);
 }
 
+int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs, int block, int tile) {
+  // Mirrors launch_spmm_wave_per_row_tile and launch_row_of_tiles for 16-byte aligned operands.
+  const int64_t wpb = block / 32;
+  const bool pow2_row = n_rhs >= 4 && n_rhs <= 128 && (n_rhs & (n_rhs - 1)) == 0;
+  if (!pow2_row) return max1(ceil_div(rows * ceil_div(n_rhs, tile), wpb));
+  if (n_rhs > 32) return max1(ceil_div(rows, wpb));
+  const int64_t G = n_rhs / 4, mean = rows > 0 ? nnz / rows : 0;
+  int64_t lanes = G > 4 ? G : 4;
+  while (lanes < 32 && (lanes / G) * 4 < mean) lanes *= 2;
+  return max1(ceil_div(ceil_div(rows, 32 / lanes), wpb));
+}
+
 cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block, int64_t chunk,
                                             cudaStream_t s, int64_t *launches) {
   // Zero fill of the flattened output, then the atomic schedule.

@@ -504,6 +504,8 @@ int swb_launch_shape_query(swb_context *ctx, const swb_options *o, int64_t rows,
         break;
     }
     r.physical_grid = r.logical_grid;
+    if (o->spmm_mapping == SWB_WAVE_PER_ROW_TILE)  // rows of B of 4 ... 128 floats: the tiles of a row are fused
+      r.physical_grid = swb::wave_per_row_tile_physical_grid(rows, nnz, n_rhs, (int)B, (int)o->spmm_tile_size);
   }
   *out = r;
   return SWB_OK;

@@ -88,6 +88,8 @@ cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block,
 cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block,
                                           int tile, cudaStream_t s,
                                           int64_t *launches);
+// CUDA blocks launch_spmm_wave_per_row_tile uses when B and C are 16-byte aligned.
+int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs, int block, int tile);
 cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block,
                                             int64_t chunk, cudaStream_t s,
                                             int64_t *launches);

@@ -139,10 +139,13 @@ def test_launch_shapes_follow_reference_grid_arithmetic():
     # C2: 65536 rows, N = 4, tile 4, block 64 -> 65536 units, 32768 blocks
     s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=4 spmm-block-size=64", 65536, 2097152, 4)
     assert (s.work_units, s.logical_grid) == (65536, 32768)
+    assert s.physical_grid == 8192  # 32 nnz per row: 8 lanes per row, 4 rows per warp, 2 warps per block
+    s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", 2097152, 134217728, 64)
+    assert (s.work_units, s.logical_grid, s.physical_grid) == (4 * 2097152, 1048576, 262144)  # tiles of a row fused
     s = swb.launch_shape("spmm-mapping=thread-per-output spmm-block-size=64", 65536, 2097152, 4)
     assert s.logical_grid == 4096
     s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=64", 100, 1000, 70)
-    assert s.work_units == 500  # ceil(70 / 16) = 5 tiles per row
+    assert s.work_units == 500 and s.physical_grid == s.logical_grid == 250  # ceil(70 / 16) = 5 tiles per row
 
 
 def test_shard_rows_by_nnz():
