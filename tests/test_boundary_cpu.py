@@ -207,3 +207,18 @@ def test_plan_row_panels():
     cuts = plan_row_panels(giant, 1000)
     assert cuts[0] == 0 and cuts[-1] == 21 and np.all(np.diff(cuts) > 0)
     assert list(plan_row_panels(np.zeros(1, np.int32), 4)) == [0, 0]  # no rows
+
+
+def test_headers_are_plain_c(tmp_path):
+    """Both public headers compile as C99 (the boundary is a C ABI: no C++ or torch types in it) and as C++."""
+    import shutil
+    import subprocess
+    src = tmp_path / "include_check.c"
+    src.write_text('#include "sparsewave_b200.h"\n#include "sparsewave_benchmark_utils.h"\n'
+                   "int main(void) { swb_options o; swb_options_default(&o); return 0; }\n")
+    gcc, gxx = shutil.which("gcc"), shutil.which("g++")
+    if not gcc or not gxx:
+        pytest.skip("no host compiler")
+    inc = str(ROOT / "include")
+    subprocess.run([gcc, "-std=c99", "-pedantic", "-Werror", "-Wall", "-I", inc, "-fsyntax-only", str(src)], check=True)
+    subprocess.run([gxx, "-std=c++17", "-Werror", "-Wall", "-I", inc, "-fsyntax-only", "-x", "c++", str(src)], check=True)
