@@ -259,8 +259,11 @@ SWB_API int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *opts,
  * and then call the operator in a loop (benchmark/spmv.mlir.in:37-65).
  * swb_csr_upload checks the index arrays (as swb_check_csr_host does) and
  * copies the matrix; the per-call functions copy x (or B) in, run the kernel,
- * copy y (or C) out and synchronise.  The handle belongs to the context's
- * device and is released with swb_csr_release. */
+ * copy y (or C) out and synchronise.  Large matrices are cut into row panels
+ * at upload (swb_plan_row_panels) and the rows of the result start their copy
+ * to the host as soon as their panel is done, while later panels compute; use
+ * pinned host buffers to benefit.  The handle belongs to the context's device
+ * and is released with swb_csr_release. */
 typedef struct swb_csr_handle swb_csr_handle;
 SWB_API int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols,
                            int64_t nnz, const int32_t *row_ptr,
