@@ -261,7 +261,10 @@ SWB_API int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *opts,
  * copies the matrix; the per-call functions copy x (or B) in, run the kernel,
  * copy y (or C) out and synchronise.  Large matrices are cut into row panels
  * at upload (swb_plan_row_panels) and the rows of the result start their copy
- * to the host as soon as their panel is done, while later panels compute; use
+ * to the host as soon as their panel is done, while later panels compute;
+ * matrices of 40 M nonzeros or more (SWB_RESIDENT_SPLIT_NNZ) are also kept as
+ * two column halves (twice the device memory) so that the first half computes
+ * while the second half of the dense operand is still being copied in.  Use
  * pinned host buffers to benefit.  The handle belongs to the context's device
  * and is released with swb_csr_release. */
 typedef struct swb_csr_handle swb_csr_handle;

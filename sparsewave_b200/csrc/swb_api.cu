@@ -27,6 +27,9 @@ struct swb_context {
   // Result copies of the resident-matrix host calls run here, behind the kernels of later row panels.
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t panel_done[8] = {};
+  // The dense operand of those calls travels here in two halves.
+  cudaStream_t upload_stream = nullptr;
+  cudaEvent_t upload_done[2] = {};
   int *status_flag = nullptr;  // device int for kernels with bounded waits
   void *comm = nullptr;        // NCCL communicator of the multi-GPU path (swb_comm.cu)
   void *peer_window = nullptr; // peer-store all-gather window (swb_peer_window.cu)
@@ -170,8 +173,11 @@ int ensure_host_stream(swb_context *ctx) {
 int ensure_copy_stream(swb_context *ctx) {
   if (ctx->copy_stream) return SWB_OK;
   cudaError_t e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->upload_stream, cudaStreamNonBlocking);
   for (int k = 0; e == cudaSuccess && k < 8; ++k)
     e = cudaEventCreateWithFlags(&ctx->panel_done[k], cudaEventDisableTiming);
+  for (int k = 0; e == cudaSuccess && k < 2; ++k)
+    e = cudaEventCreateWithFlags(&ctx->upload_done[k], cudaEventDisableTiming);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamCreate(copy)");
   return SWB_OK;
 }
@@ -242,7 +248,10 @@ void swb_destroy(swb_context *ctx) {
   if (ctx->status_flag) cudaFree(ctx->status_flag);
   if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
   if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+  if (ctx->upload_stream) cudaStreamDestroy(ctx->upload_stream);
   for (cudaEvent_t ev : ctx->panel_done)
+    if (ev) cudaEventDestroy(ev);
+  for (cudaEvent_t ev : ctx->upload_done)
     if (ev) cudaEventDestroy(ev);
   delete ctx;
 }
@@ -824,16 +833,29 @@ int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *o, int64_t rows,
 // panel below which a call runs uncut, default 524288), both read at upload.
 constexpr int kMaxPanels = 8;
 
-struct swb_csr_handle {
-  int64_t rows, cols, nnz;
-  int32_t *row_ptr, *col_idx;
-  float *val;
+// Column halves.  A large matrix is also stored as two matrices over the same rows, one with the entries
+// whose column lies below cols/2 and one with the rest.  A call on a mapping that can accumulate then sends
+// the first half of the dense operand, runs the first matrix while the second half is still on its way,
+// and adds the second matrix (cut into row panels, as above) on top.  SWB_RESIDENT_SPLIT_NNZ: nnz from
+// which a matrix is stored this way (default 40000000; it doubles the matrix's device memory).
+struct CsrPart {
+  int64_t nnz = 0;
+  int32_t *row_ptr = nullptr, *col_idx = nullptr;
+  float *val = nullptr;
   int panels = 1;
   int64_t panel_row[kMaxPanels + 1] = {};     // first row of each panel, then rows
   int64_t panel_pos[kMaxPanels + 1] = {};     // row_ptr[panel_row[k]]
   int64_t panel_rp_off[kMaxPanels] = {};      // start of panel k's rebased row offsets inside panel_row_ptr
   int32_t *panel_row_ptr = nullptr;           // device
+};
+
+struct swb_csr_handle {
+  int64_t rows = 0, cols = 0, nnz = 0;
   int64_t panel_min_bytes = 0;
+  CsrPart whole;
+  bool split = false;
+  int64_t split_col = 0;
+  CsrPart low, high;  // columns [0, split_col) and [split_col, cols)
 };
 
 namespace {
@@ -866,6 +888,41 @@ int plan_panels(int64_t rows, int64_t nnz, const int32_t *row_ptr, int64_t panel
   return count;
 }
 
+void free_part(CsrPart &p) {
+  cudaFree(p.row_ptr); cudaFree(p.col_idx); cudaFree(p.val); cudaFree(p.panel_row_ptr);
+  p = CsrPart();
+}
+
+// Copies one CSR matrix to the device and, when panel_nnz > 0, plans and stores its row panels.
+cudaError_t upload_part(CsrPart &p, int64_t rows, int64_t nnz, const int32_t *row_ptr, const int32_t *col_idx,
+                        const float *val, int64_t panel_nnz) {
+  p.nnz = nnz;
+  p.panel_row[1] = rows;
+  p.panel_pos[1] = nnz;
+  cudaError_t e = cudaMalloc(&p.row_ptr, (size_t)(rows + 1) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&p.col_idx, (size_t)(nnz > 0 ? nnz : 1) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&p.val, (size_t)(nnz > 0 ? nnz : 1) * 4);
+  if (e == cudaSuccess) e = cudaMemcpy(p.row_ptr, row_ptr, (size_t)(rows + 1) * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(p.col_idx, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(p.val, val, (size_t)nnz * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess || panel_nnz <= 0 || rows <= 0 || nnz <= 0) return e;
+  const int count = plan_panels(rows, nnz, row_ptr, panel_nnz, p.panel_row);
+  if (count <= 1) return e;
+  std::vector<int32_t> rebased;
+  for (int k = 0; k < count; ++k) {
+    const int64_t r0 = p.panel_row[k], r1 = p.panel_row[k + 1];
+    p.panel_pos[k] = row_ptr[r0];
+    p.panel_rp_off[k] = (int64_t)rebased.size();
+    for (int64_t r = r0; r <= r1; ++r) rebased.push_back(row_ptr[r] - row_ptr[r0]);
+    while (rebased.size() % 64) rebased.push_back(0);  // every panel's offsets start 256-byte aligned
+  }
+  p.panel_pos[count] = nnz;
+  e = cudaMalloc(&p.panel_row_ptr, rebased.size() * 4);
+  if (e == cudaSuccess) e = cudaMemcpy(p.panel_row_ptr, rebased.data(), rebased.size() * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) p.panels = count;
+  return e;
+}
+
 }  // namespace
 
 int swb_plan_row_panels(int64_t rows, int64_t nnz, const int32_t *row_ptr, int64_t panel_nnz, int64_t *panel_rows) {
@@ -887,37 +944,40 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
   if (nnz > 0 && !val) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: NULL operand pointer");
   swb_csr_handle *h = new swb_csr_handle();
   h->rows = rows; h->cols = cols; h->nnz = nnz;
-  h->row_ptr = h->col_idx = nullptr; h->val = nullptr;
-  cudaError_t e = cudaMalloc(&h->row_ptr, (size_t)(rows + 1) * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&h->col_idx, (size_t)(nnz > 0 ? nnz : 1) * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&h->val, (size_t)(nnz > 0 ? nnz : 1) * 4);
-  if (e == cudaSuccess) e = cudaMemcpy(h->row_ptr, row_ptr, (size_t)(rows + 1) * 4, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(h->col_idx, col_idx, (size_t)nnz * 4, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess && nnz > 0) e = cudaMemcpy(h->val, val, (size_t)nnz * 4, cudaMemcpyHostToDevice);
-
-  // Row panels for the pipelined result copy.
   h->panel_min_bytes = env_i64("SWB_RESIDENT_PANEL_BYTES", 512 * 1024);
-  h->panel_row[1] = rows;
-  h->panel_pos[1] = nnz;
-  if (e == cudaSuccess && rows > 0 && nnz > 0) {
-    const int count = plan_panels(rows, nnz, row_ptr, env_i64("SWB_RESIDENT_PANEL_NNZ", 20000000), h->panel_row);
-    if (count > 1) {
-      std::vector<int32_t> rebased;
-      for (int k = 0; k < count; ++k) {
-        const int64_t r0 = h->panel_row[k], r1 = h->panel_row[k + 1];
-        h->panel_pos[k] = row_ptr[r0];
-        h->panel_rp_off[k] = (int64_t)rebased.size();
-        for (int64_t r = r0; r <= r1; ++r) rebased.push_back(row_ptr[r] - row_ptr[r0]);
-        while (rebased.size() % 64) rebased.push_back(0);  // every panel's offsets start 256-byte aligned
+  const int64_t panel_nnz = env_i64("SWB_RESIDENT_PANEL_NNZ", 20000000);
+  cudaError_t e = upload_part(h->whole, rows, nnz, row_ptr, col_idx, val, panel_nnz);
+
+  if (e == cudaSuccess && rows > 0 && cols >= 2 && nnz >= env_i64("SWB_RESIDENT_SPLIT_NNZ", 40000000)) {
+    // The two column halves, each a CSR matrix over all rows with the entries in their original order.
+    const int64_t mid = cols / 2;
+    std::vector<int32_t> rp_lo(rows + 1, 0), rp_hi(rows + 1, 0);
+    for (int64_t r = 0; r < rows; ++r) {
+      int32_t below = 0;
+      for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) below += col_idx[p] < mid;
+      rp_lo[r + 1] = rp_lo[r] + below;
+      rp_hi[r + 1] = rp_hi[r] + (row_ptr[r + 1] - row_ptr[r] - below);
+    }
+    const int64_t nnz_lo = rp_lo[rows], nnz_hi = rp_hi[rows];
+    std::vector<int32_t> ci_lo(nnz_lo), ci_hi(nnz_hi);
+    std::vector<float> v_lo(nnz_lo), v_hi(nnz_hi);
+    for (int64_t r = 0; r < rows; ++r) {
+      int64_t a = rp_lo[r], b = rp_hi[r];
+      for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
+        if (col_idx[p] < mid) { ci_lo[a] = col_idx[p]; v_lo[a++] = val[p]; }
+        else { ci_hi[b] = col_idx[p]; v_hi[b++] = val[p]; }
       }
-      h->panel_pos[count] = nnz;
-      e = cudaMalloc(&h->panel_row_ptr, rebased.size() * 4);
-      if (e == cudaSuccess) e = cudaMemcpy(h->panel_row_ptr, rebased.data(), rebased.size() * 4, cudaMemcpyHostToDevice);
-      if (e == cudaSuccess) h->panels = count;
+    }
+    e = upload_part(h->low, rows, nnz_lo, rp_lo.data(), ci_lo.data(), v_lo.data(), 0);
+    // the second half finishes the result, so it is the one cut into row panels (about as many as the whole)
+    if (e == cudaSuccess) e = upload_part(h->high, rows, nnz_hi, rp_hi.data(), ci_hi.data(), v_hi.data(), (panel_nnz + 1) / 2);
+    if (e == cudaSuccess) {
+      h->split = true;
+      h->split_col = mid;
     }
   }
   if (e != cudaSuccess) {
-    cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val); cudaFree(h->panel_row_ptr);
+    free_part(h->whole); free_part(h->low); free_part(h->high);
     delete h;
     return cuda_fail(ctx, e, "csr upload");
   }
@@ -928,19 +988,40 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
 void swb_csr_release(swb_context *ctx, swb_csr_handle *h) {
   if (!h) return;
   if (ctx) cudaSetDevice(ctx->device);
-  cudaFree(h->row_ptr); cudaFree(h->col_idx); cudaFree(h->val); cudaFree(h->panel_row_ptr);
+  free_part(h->whole); free_part(h->low); free_part(h->high);
   delete h;
 }
 
 extern "C++" {
 namespace {
 
-// Shared body of the two resident host calls.  `width` = floats per row of the dense operand and of the
-// result (1 for SpMV); `launch(rows, nnz, row_ptr, col, val, out)` queues one operator call on the
-// host stream.
+// Queues the operator on `part` panel by panel on the host stream; behind each panel its rows of the
+// result start their copy to the host on the copy stream.
 template <typename Launch>
-int resident_host_call(swb_context *ctx, const swb_csr_handle *h, int64_t width, const float *dense_host,
-                       float *out_host, float **d_dense_out, Launch launch) {
+int run_panels_with_copy(swb_context *ctx, const swb_options *o, const CsrPart &part, int64_t width, float *d_out,
+                         float *out_host, cudaError_t &e, Launch &launch) {
+  int st = SWB_OK;
+  for (int k = 0; k < part.panels && e == cudaSuccess; ++k) {
+    const int64_t r0 = part.panel_row[k], r1 = part.panel_row[k + 1], p0 = part.panel_pos[k];
+    const int32_t *rp = part.panels > 1 ? part.panel_row_ptr + part.panel_rp_off[k] : part.row_ptr;
+    st = launch(o, r1 - r0, part.panel_pos[k + 1] - p0, rp, part.col_idx + p0, part.val + p0, d_out + r0 * width);
+    if (st != SWB_OK) break;
+    e = cudaEventRecord(ctx->panel_done[k], ctx->host_stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy_stream, ctx->panel_done[k], 0);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(out_host + r0 * width, d_out + r0 * width, (size_t)(r1 - r0) * width * 4,
+                          cudaMemcpyDeviceToHost, ctx->copy_stream);
+  }
+  return st;
+}
+
+// Shared body of the two resident host calls.  `width` = floats per row of the dense operand and of the
+// result (1 for SpMV); `can_accumulate` = the chosen mapping can add to an existing result;
+// `launch(opts, rows, nnz, row_ptr, col, val, out)` queues one operator call on the host stream.
+template <typename Launch>
+int resident_host_call(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, int64_t width,
+                       bool can_accumulate, const float *dense_host, float *out_host, float **d_dense_out,
+                       Launch launch) {
   int st = ensure_host_stream(ctx);
   if (st != SWB_OK) return st;
   const size_t dense_bytes = (size_t)h->cols * width * 4, out_bytes = (size_t)h->rows * width * 4;
@@ -950,10 +1031,12 @@ int resident_host_call(swb_context *ctx, const swb_csr_handle *h, int64_t width,
   float *d_out = workspace_take<float>(ctx, h->rows * width);
   *d_dense_out = d_dense;
   cudaStream_t s = ctx->host_stream;
-  if (dense_bytes > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_dense, dense_host, dense_bytes, cudaMemcpyHostToDevice, s));
-  const bool cut = h->panels > 1 && (int64_t)(out_bytes / h->panels) >= h->panel_min_bytes;
-  if (!cut) {
-    st = launch(h->rows, h->nnz, h->row_ptr, h->col_idx, h->val, d_out);
+  const bool halves = h->split && can_accumulate && !o->accumulate && out_bytes > 0;
+  const CsrPart &last = halves ? h->high : h->whole;
+  const bool cut = last.panels > 1 && (int64_t)(out_bytes / last.panels) >= h->panel_min_bytes;
+  if (!halves && !cut) {
+    if (dense_bytes > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_dense, dense_host, dense_bytes, cudaMemcpyHostToDevice, s));
+    st = launch(o, h->rows, h->nnz, h->whole.row_ptr, h->whole.col_idx, h->whole.val, d_out);
     if (st != SWB_OK) return st;
     if (out_bytes > 0) SWB_CUDA(ctx, cudaMemcpyAsync(out_host, d_out, out_bytes, cudaMemcpyDeviceToHost, s));
     SWB_CUDA(ctx, cudaStreamSynchronize(s));
@@ -962,21 +1045,39 @@ int resident_host_call(swb_context *ctx, const swb_csr_handle *h, int64_t width,
   st = ensure_copy_stream(ctx);
   if (st != SWB_OK) return st;
   cudaError_t e = cudaSuccess;
-  for (int k = 0; k < h->panels && st == SWB_OK && e == cudaSuccess; ++k) {
-    const int64_t r0 = h->panel_row[k], r1 = h->panel_row[k + 1], p0 = h->panel_pos[k];
-    st = launch(r1 - r0, h->panel_pos[k + 1] - p0, h->panel_row_ptr + h->panel_rp_off[k], h->col_idx + p0,
-                h->val + p0, d_out + r0 * width);
-    if (st != SWB_OK) break;
-    e = cudaEventRecord(ctx->panel_done[k], s);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy_stream, ctx->panel_done[k], 0);
+  if (!halves) {
+    e = cudaMemcpyAsync(d_dense, dense_host, dense_bytes, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) st = run_panels_with_copy(ctx, o, h->whole, width, d_out, out_host, e, launch);
+  } else {
+    // first half of the operand, first matrix; the second half travels meanwhile; second matrix on top
+    const size_t first = (size_t)h->split_col * width * 4;
+    cudaStream_t up = ctx->upload_stream;
+    e = cudaMemcpyAsync(d_dense, dense_host, first, cudaMemcpyHostToDevice, up);
+    if (e == cudaSuccess) e = cudaEventRecord(ctx->upload_done[0], up);
     if (e == cudaSuccess)
-      e = cudaMemcpyAsync(out_host + r0 * width, d_out + r0 * width, (size_t)(r1 - r0) * width * 4,
-                          cudaMemcpyDeviceToHost, ctx->copy_stream);
+      e = cudaMemcpyAsync(reinterpret_cast<char *>(d_dense) + first, reinterpret_cast<const char *>(dense_host) + first,
+                          dense_bytes - first, cudaMemcpyHostToDevice, up);
+    if (e == cudaSuccess) e = cudaEventRecord(ctx->upload_done[1], up);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, ctx->upload_done[0], 0);
+    if (e == cudaSuccess)
+      st = launch(o, h->rows, h->low.nnz, h->low.row_ptr, h->low.col_idx, h->low.val, d_out);
+    if (e == cudaSuccess && st == SWB_OK) e = cudaStreamWaitEvent(s, ctx->upload_done[1], 0);
+    if (e == cudaSuccess && st == SWB_OK) {
+      swb_options add = *o;
+      add.accumulate = 1;
+      if (cut) {
+        st = run_panels_with_copy(ctx, &add, h->high, width, d_out, out_host, e, launch);
+      } else {
+        st = launch(&add, h->rows, h->high.nnz, h->high.row_ptr, h->high.col_idx, h->high.val, d_out);
+        if (st == SWB_OK) e = cudaMemcpyAsync(out_host, d_out, out_bytes, cudaMemcpyDeviceToHost, s);
+      }
+    }
   }
-  // Both streams are drained before returning, also after an error: the copies write caller memory.
+  // Every stream is drained before returning, also after an error: the copies touch caller memory.
+  const cudaError_t e0 = ctx->upload_stream ? cudaStreamSynchronize(ctx->upload_stream) : cudaSuccess;
   const cudaError_t e1 = cudaStreamSynchronize(s), e2 = cudaStreamSynchronize(ctx->copy_stream);
   if (st != SWB_OK) return st;
-  if (e == cudaSuccess) e = e1 != cudaSuccess ? e1 : e2;
+  if (e == cudaSuccess) e = e0 != cudaSuccess ? e0 : (e1 != cudaSuccess ? e1 : e2);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "resident host call");
   return SWB_OK;
 }
@@ -987,13 +1088,14 @@ int resident_host_call(swb_context *ctx, const swb_csr_handle *h, int64_t width,
 int swb_spmv_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, const float *x, float *y) {
   int st = check_ctx(ctx);
   if (st != SWB_OK) return st;
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
   if (!h || (h->cols > 0 && !x) || (h->rows > 0 && !y))
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: NULL matrix handle or operand pointer");
   float *d_x = nullptr;
-  return resident_host_call(ctx, h, 1, x, y, &d_x,
-                            [&](int64_t rows, int64_t nnz, const int32_t *rp, const int32_t *ci, const float *v,
-                                float *d_y) {
-                              return swb_spmv(ctx, o, rows, h->cols, nnz, rp, ci, v, d_x, d_y, ctx->host_stream);
+  return resident_host_call(ctx, o, h, 1, is_position_mapping(o->mapping), x, y, &d_x,
+                            [&](const swb_options *opts, int64_t rows, int64_t nnz, const int32_t *rp,
+                                const int32_t *ci, const float *v, float *d_y) {
+                              return swb_spmv(ctx, opts, rows, h->cols, nnz, rp, ci, v, d_x, d_y, ctx->host_stream);
                             });
 }
 
@@ -1001,14 +1103,15 @@ int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr
                            const float *B, float *C) {
   int st = check_ctx(ctx);
   if (st != SWB_OK) return st;
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
   if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
   if (!h || (h->cols > 0 && !B) || (h->rows > 0 && !C))
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL matrix handle or operand pointer");
   float *d_B = nullptr;
-  return resident_host_call(ctx, h, n_rhs, B, C, &d_B,
-                            [&](int64_t rows, int64_t nnz, const int32_t *rp, const int32_t *ci, const float *v,
-                                float *d_C) {
-                              return swb_spmm(ctx, o, rows, h->cols, nnz, n_rhs, rp, ci, v, d_B, d_C,
+  return resident_host_call(ctx, o, h, n_rhs, o->spmm_mapping != SWB_THREAD_PER_OUTPUT, B, C, &d_B,
+                            [&](const swb_options *opts, int64_t rows, int64_t nnz, const int32_t *rp,
+                                const int32_t *ci, const float *v, float *d_C) {
+                              return swb_spmm(ctx, opts, rows, h->cols, nnz, n_rhs, rp, ci, v, d_B, d_C,
                                               ctx->host_stream);
                             });
 }

@@ -171,13 +171,16 @@ ALL_SPMV = ["mapping=thread-per-row", "mapping=wave-per-row block-size=128", "ma
             "mapping=wave-per-position", "mapping=wave-per-position wave-position-batch=1"]
 
 
-def test_resident_matrix_row_panels(ctx, monkeypatch):
-    """A resident matrix cut into row panels (result rows copied out while later panels run) gives the
-    result of the uncut call: every SpMV mapping, SpMM with aligned and ragged widths, rows of very
-    different lengths and empty rows around the cuts."""
+@pytest.mark.parametrize("halves", [False, True])
+def test_resident_matrix_row_panels(ctx, monkeypatch, halves):
+    """A resident matrix cut into row panels (result rows copied out while later panels run) and, with
+    `halves`, also stored as two column halves (first half of the dense operand used while the second is
+    still being copied in) gives the result of the plain call: every SpMV mapping, SpMM with aligned and
+    ragged widths, rows of very different lengths and empty rows around the cuts."""
     from sparsewave_b200.api import plan_row_panels
     monkeypatch.setenv("SWB_RESIDENT_PANEL_NNZ", "2000")
     monkeypatch.setenv("SWB_RESIDENT_PANEL_BYTES", "1")
+    monkeypatch.setenv("SWB_RESIDENT_SPLIT_NNZ", "1000" if halves else "1000000000")
     rng = np.random.default_rng(21)
     rows, cols = 4000, 3000
     lens = rng.integers(0, 12, rows)
