@@ -263,8 +263,8 @@ SWB_API int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *opts,
  * at upload (swb_plan_row_panels) and the rows of the result start their copy
  * to the host as soon as their panel is done, while later panels compute;
  * matrices of 40 M nonzeros or more (SWB_RESIDENT_SPLIT_NNZ) are also kept as
- * two column halves (twice the device memory) so that the first half computes
- * while the second half of the dense operand is still being copied in.  Use
+ * two column parts (twice the device memory) so that the first part computes
+ * while the rest of the dense operand is still being copied in.  Use
  * pinned host buffers to benefit.  The handle belongs to the context's device
  * and is released with swb_csr_release. */
 typedef struct swb_csr_handle swb_csr_handle;

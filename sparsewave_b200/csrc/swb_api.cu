@@ -833,8 +833,8 @@ int swb_bsr_spmm_bf16_host(swb_context *ctx, const swb_options *o, int64_t rows,
 // panel below which a call runs uncut, default 524288), both read at upload.
 constexpr int kMaxPanels = 8;
 
-// Column halves.  A large matrix is also stored as two matrices over the same rows, one with the entries
-// whose column lies below cols/2 and one with the rest.  A call on a mapping that can accumulate then sends
+// Column parts.  A large matrix is also stored as two matrices over the same rows, one with the entries
+// whose column lies below a cut (36 % of the columns by default) and one with the rest.  A call on a mapping that can accumulate then sends
 // the first half of the dense operand, runs the first matrix while the second half is still on its way,
 // and adds the second matrix (cut into row panels, as above) on top.  SWB_RESIDENT_SPLIT_NNZ: nnz from
 // which a matrix is stored this way (default 40000000; it doubles the matrix's device memory).
@@ -950,7 +950,15 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
 
   if (e == cudaSuccess && rows > 0 && cols >= 2 && nnz >= env_i64("SWB_RESIDENT_SPLIT_NNZ", 40000000)) {
     // The two column halves, each a CSR matrix over all rows with the entries in their original order.
-    const int64_t mid = cols / 2;
+    // Where the columns are cut: the first part should finish computing about when the rest of the operand
+    // has arrived (SWB_RESIDENT_SPLIT_PERCENT of the columns go to the first part; 33 and 40 measured best
+    // on a 92 M-nonzero SpMV over PCIe gen 5, 25 and 50 cost 6 % more).
+    int64_t percent = env_i64("SWB_RESIDENT_SPLIT_PERCENT", 36);
+    if (percent > 90) percent = 90;
+    if (percent < 10) percent = 10;
+    int64_t mid = (int64_t)((__int128)cols * percent / 100);
+    mid -= mid % 4;  // the second part of the operand starts 16-byte aligned
+    if (mid < 1) mid = 1;
     std::vector<int32_t> rp_lo(rows + 1, 0), rp_hi(rows + 1, 0);
     for (int64_t r = 0; r < rows; ++r) {
       int32_t below = 0;
