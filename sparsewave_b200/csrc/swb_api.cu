@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <new>
 #include <string>
 #include <vector>
 
@@ -949,7 +950,8 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
   cudaError_t e = upload_part(h->whole, rows, nnz, row_ptr, col_idx, val, panel_nnz);
 
   if (e == cudaSuccess && rows > 0 && cols >= 2 && nnz >= env_i64("SWB_RESIDENT_SPLIT_NNZ", 40000000)) {
-    // The two column halves, each a CSR matrix over all rows with the entries in their original order.
+    // The two column parts, each a CSR matrix over all rows with the entries in their original order.  They
+    // are an optimisation: without the host or device memory for them the matrix stays resident uncut.
     // Where the columns are cut: the first part should finish computing about when the rest of the operand
     // has arrived (SWB_RESIDENT_SPLIT_PERCENT of the columns go to the first part; 33 and 40 measured best
     // on a 92 M-nonzero SpMV over PCIe gen 5, 25 and 50 cost 6 % more).
@@ -959,29 +961,40 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
     int64_t mid = (int64_t)((__int128)cols * percent / 100);
     mid -= mid % 4;  // the second part of the operand starts 16-byte aligned
     if (mid < 1) mid = 1;
-    std::vector<int32_t> rp_lo(rows + 1, 0), rp_hi(rows + 1, 0);
-    for (int64_t r = 0; r < rows; ++r) {
-      int32_t below = 0;
-      for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) below += col_idx[p] < mid;
-      rp_lo[r + 1] = rp_lo[r] + below;
-      rp_hi[r + 1] = rp_hi[r] + (row_ptr[r + 1] - row_ptr[r] - below);
-    }
-    const int64_t nnz_lo = rp_lo[rows], nnz_hi = rp_hi[rows];
-    std::vector<int32_t> ci_lo(nnz_lo), ci_hi(nnz_hi);
-    std::vector<float> v_lo(nnz_lo), v_hi(nnz_hi);
-    for (int64_t r = 0; r < rows; ++r) {
-      int64_t a = rp_lo[r], b = rp_hi[r];
-      for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
-        if (col_idx[p] < mid) { ci_lo[a] = col_idx[p]; v_lo[a++] = val[p]; }
-        else { ci_hi[b] = col_idx[p]; v_hi[b++] = val[p]; }
+    try {
+      std::vector<int32_t> rp_lo(rows + 1, 0), rp_hi(rows + 1, 0);
+      for (int64_t r = 0; r < rows; ++r) {
+        int32_t below = 0;
+        for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) below += col_idx[p] < mid;
+        rp_lo[r + 1] = rp_lo[r] + below;
+        rp_hi[r + 1] = rp_hi[r] + (row_ptr[r + 1] - row_ptr[r] - below);
       }
+      const int64_t nnz_lo = rp_lo[rows], nnz_hi = rp_hi[rows];
+      std::vector<int32_t> ci_lo(nnz_lo), ci_hi(nnz_hi);
+      std::vector<float> v_lo(nnz_lo), v_hi(nnz_hi);
+      for (int64_t r = 0; r < rows; ++r) {
+        int64_t a = rp_lo[r], b = rp_hi[r];
+        for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
+          if (col_idx[p] < mid) { ci_lo[a] = col_idx[p]; v_lo[a++] = val[p]; }
+          else { ci_hi[b] = col_idx[p]; v_hi[b++] = val[p]; }
+        }
+      }
+      cudaError_t es = upload_part(h->low, rows, nnz_lo, rp_lo.data(), ci_lo.data(), v_lo.data(), 0);
+      // the second part finishes the result, so it is the one cut into row panels (about as many as the whole)
+      if (es == cudaSuccess)
+        es = upload_part(h->high, rows, nnz_hi, rp_hi.data(), ci_hi.data(), v_hi.data(), (panel_nnz + 1) / 2);
+      if (es == cudaSuccess) {
+        h->split = true;
+        h->split_col = mid;
+      } else {
+        cudaGetLastError();  // out of device memory for the second copy: not an error of the upload
+      }
+    } catch (const std::bad_alloc &) {
+      // no host memory for the temporary copies: the matrix stays uncut
     }
-    e = upload_part(h->low, rows, nnz_lo, rp_lo.data(), ci_lo.data(), v_lo.data(), 0);
-    // the second half finishes the result, so it is the one cut into row panels (about as many as the whole)
-    if (e == cudaSuccess) e = upload_part(h->high, rows, nnz_hi, rp_hi.data(), ci_hi.data(), v_hi.data(), (panel_nnz + 1) / 2);
-    if (e == cudaSuccess) {
-      h->split = true;
-      h->split_col = mid;
+    if (!h->split) {
+      free_part(h->low);
+      free_part(h->high);
     }
   }
   if (e != cudaSuccess) {
