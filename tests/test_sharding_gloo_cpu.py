@@ -123,3 +123,31 @@ def test_split_by_column_ownership():
         r = p.row_ptr.numpy()
         c = p.col_idx.numpy()
         assert all(np.all(np.diff(c[r[i]:r[i + 1]]) > 0) for i in range(p.rows))
+
+
+def test_split_by_column_range_keeps_every_entry_once():
+    """The column-ownership split of a shard (the overlapped operator's two passes): both parts keep all rows
+    and the order of the entries inside a row, and together they are the shard."""
+    rows, cols = 300, 120
+    rp, ci, v = random_csr(rows, cols, 8, seed=31, empty_fraction=0.25)
+    shard = sharding.shard_csr(torch.from_numpy(rp), torch.from_numpy(ci), torch.from_numpy(v), cols, 0, 1)
+    inside, outside = sharding.split_by_column_range(shard, 40, 80)
+    assert inside.rows == outside.rows == rows and inside.nnz + outside.nnz == len(v)
+    assert bool(((inside.col_idx >= 40) & (inside.col_idx < 80)).all())
+    assert bool(((outside.col_idx < 40) | (outside.col_idx >= 80)).all())
+    x = np.random.default_rng(31).uniform(-1, 1, cols).astype(np.float32)
+    parts = [oracle.csr_spmv(p.row_ptr.numpy(), p.col_idx.numpy(), p.values.numpy(), x) for p in (inside, outside)]
+    whole = oracle.csr_spmv(rp, ci, v, x)
+    assert np.allclose(parts[0] + parts[1], whole, rtol=1e-5, atol=1e-5)
+    for r in range(rows):  # order inside a row is the original order
+        row_cols = ci[rp[r]:rp[r + 1]]
+        a = inside.col_idx[inside.row_ptr[r]:inside.row_ptr[r + 1]].numpy()
+        b = outside.col_idx[outside.row_ptr[r]:outside.row_ptr[r + 1]].numpy()
+        assert np.array_equal(a, row_cols[(row_cols >= 40) & (row_cols < 80)])
+        assert np.array_equal(b, row_cols[(row_cols < 40) | (row_cols >= 80)])
+
+
+def test_window_bytes():
+    assert sharding.window_bytes(4194304, 8) == 524288 * 4
+    assert sharding.window_bytes(701, 2, (3,)) == 351 * 3 * 4
+    assert sharding.window_bytes(16384, 4, (512,), 2) == 4096 * 512 * 2
