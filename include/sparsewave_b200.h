@@ -157,6 +157,18 @@ SWB_API int swb_spmv(swb_context *ctx, const swb_options *opts, int64_t rows,
                      const int32_t *col_idx, const float *val, const float *x,
                      float *y, swb_stream stream);
 
+/* Roofline probe for SpMV, not an operator: streams col_idx and val (nnz
+ * rounded down to a multiple of 4; both arrays 16-byte aligned) and gathers
+ * x[col_idx[p]] with no row logic, adding the products into the 1024 floats at
+ * `sink`.  Its time on a matrix's own arrays is the floor of any mapping that
+ * reads x through the cache hierarchy; the benchmark reports it beside the
+ * kernel's time (the analogue of the reference runner's per-kernel bandwidth
+ * columns, benchmark/run_spmv_benchmark.py:31-61).  No reference counterpart. */
+SWB_API int swb_probe_stream_gather(swb_context *ctx, int64_t nnz,
+                                    const int32_t *col_idx, const float *val,
+                                    const float *x, float *sink,
+                                    swb_stream stream);
+
 /* sparsewave.coo_spmv (SparseWaveOps.td, COOSpMVOp; lowering
  * ThreadPerNonzeroCOOSpMVPattern, SparseWaveToGPU.cpp:154-214): y is zero
  * filled, then every entry adds val[p] * x[col_idx[p]] to y[row_idx[p]];
@@ -217,9 +229,10 @@ SWB_API int swb_bsr_spmm_bf16(swb_context *ctx, const swb_options *opts,
  *   - Every call shares the array and first clears the words it uses, so it
  *     holds the outcome of the latest call only, and calls that overlap on
  *     the GPU race on it.
- *   - gave_up_ctas: NULL for an asynchronous call; otherwise the call
- *     synchronises `stream` and stores how many CTAs abandoned a wait (0 = the
- *     output is valid).
+ *   - gave_up_ctas: NULL for an asynchronous call (check it later with
+ *     swb_bsr16_static_status, before the next static call on that device);
+ *     otherwise the call synchronises `stream` and stores how many CTAs
+ *     abandoned a wait (0 = the output is valid).
  * Errors are reported through swb_last_error(NULL). */
 SWB_API int swb_bsr16_spmm_bf16_static(int64_t rows, int64_t cols, int64_t nnzb,
                                        int64_t n_rhs,
@@ -229,6 +242,13 @@ SWB_API int swb_bsr16_spmm_bf16_static(int64_t rows, int64_t cols, int64_t nnzb,
                                        const uint16_t *B, uint16_t *C,
                                        swb_stream stream,
                                        int32_t *gave_up_ctas);
+/* Outcome of the most recent swb_bsr16_spmm_bf16_static call on the current
+ * device: synchronises `stream` (the stream that call was queued on) and
+ * stores how many of its CTAs abandoned a wait (0 = its output is valid).
+ * Like that call it allocates nothing (the fixed array is read back through
+ * stack memory) and has no counterpart in the reference.  A later static call
+ * on the same device overwrites the record, so ask before making one. */
+SWB_API int swb_bsr16_static_status(swb_stream stream, int32_t *gave_up_ctas);
 
 /* ---- operators, host buffers ------------------------------------------- */
 /* Same contracts with HOST pointers: the call copies the operands to the
@@ -279,6 +299,51 @@ SWB_API int swb_spmv_resident_host(swb_context *ctx, const swb_options *opts,
 SWB_API int swb_spmm_resident_host(swb_context *ctx, const swb_options *opts,
                                    const swb_csr_handle *matrix, int64_t n_rhs,
                                    const float *B, float *C);
+
+/* ---- sharded operators -------------------------------------------------- */
+/* One row shard per rank of the context's communicator (swb_comm_init), the
+ * dense operand owned in equal contiguous chunks of ceil(cols / n_ranks) rows
+ * (rank k owns rows [k * chunk, min(cols, (k + 1) * chunk)) of x or B).  A call
+ * gathers every rank's chunk into a full copy on this device - with the
+ * peer-store kernel when the context has a window of exactly that chunk size
+ * (swb_comm_window_create), else with ncclAllGather into a buffer the context
+ * keeps - and then runs the operator on this rank's rows: y / C hold the
+ * shard's rows only.  Collective: every rank makes the same call.  The buffers
+ * are allocated by the first call that needs them (make it outside stream
+ * capture).  Without a communicator the calls are the plain operators.  Not a
+ * reference feature (the reference is single GPU).
+ *
+ * swb_spmv_sharded / swb_spmm_sharded take the shard's CSR arrays (row offsets
+ * rebased to zero, global column numbers) and this rank's chunk as DEVICE
+ * pointers and queue everything on `stream`. */
+SWB_API int swb_spmv_sharded(swb_context *ctx, const swb_options *opts,
+                             int64_t rows, int64_t cols, int64_t nnz,
+                             const int32_t *row_ptr, const int32_t *col_idx,
+                             const float *val, const float *x_owned, float *y,
+                             swb_stream stream);
+SWB_API int swb_spmm_sharded(swb_context *ctx, const swb_options *opts,
+                             int64_t rows, int64_t cols, int64_t nnz,
+                             int64_t n_rhs, const int32_t *row_ptr,
+                             const int32_t *col_idx, const float *val,
+                             const float *B_owned, float *C,
+                             swb_stream stream);
+/* swb_csr_upload_rows keeps rows [row_begin, row_end) of a HOST matrix on the
+ * device (offsets rebased to zero, checked like swb_csr_upload, one copy, no
+ * panels): the shard of a rank whose boundaries come from
+ * swb_shard_rows_by_nnz.  The *_sharded_host calls then take this rank's
+ * chunk of the dense operand and return this rank's rows in HOST memory: chunk
+ * in, exchange on the device, kernel, rows out, synchronised. */
+SWB_API int swb_csr_upload_rows(swb_context *ctx, int64_t rows_total,
+                                int64_t cols, const int32_t *row_ptr,
+                                const int32_t *col_idx, const float *val,
+                                int64_t row_begin, int64_t row_end,
+                                swb_csr_handle **out);
+SWB_API int swb_spmv_sharded_host(swb_context *ctx, const swb_options *opts,
+                                  const swb_csr_handle *shard,
+                                  const float *x_owned, float *y);
+SWB_API int swb_spmm_sharded_host(swb_context *ctx, const swb_options *opts,
+                                  const swb_csr_handle *shard, int64_t n_rhs,
+                                  const float *B_owned, float *C);
 
 /* Content checks the kernels rely on, run on HOST copies of the index arrays
  * before data is trusted: row_ptr[0] == 0, monotone, row_ptr[rows] == nnz,
@@ -422,7 +487,12 @@ SWB_API void swb_comm_destroy(swb_context *ctx);
  * by other streams while a later all-gather may overwrite it.  The kernel's
  * waits on the other ranks are bounded: if one gives up (a rank that never
  * launches its step), swb_device_status reports 3 or 4 and the window content
- * is not valid.  One window per context; capturable in a CUDA graph. */
+ * is not valid.  One window per context; capturable in a CUDA graph.
+ * swb_comm_window_destroy is collective too (every rank unmaps before any
+ * rank frees), so call it on every rank, while all ranks are still alive;
+ * swb_destroy never runs a collective: on a context that still has a window
+ * it only unmaps the peers' windows and leaves this rank's window allocated
+ * until the process ends. */
 SWB_API int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank,
                                    void **window);
 SWB_API int swb_comm_window_allgather(swb_context *ctx, const void *send,

@@ -59,6 +59,18 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Sets the thread count of the parallel loops (`parallel=True`); returns the count now in effect."""
+    lib().oracle_set_num_threads(C.c_int(int(n)))
+    return num_threads()
+
+
+def use_all_cores() -> int:
+    """One thread per core this process may run on, whatever OMP_NUM_THREADS says (multi-process
+    launchers export OMP_NUM_THREADS=1 to every rank)."""
+    return set_num_threads(len(os.sched_getaffinity(0)))
+
+
 def csr_spmv(row_ptr, col, val, x, parallel: bool = False) -> np.ndarray:
     row_ptr, col, val, x = _i32(row_ptr), _i32(col), _f32(val), _f32(x)
     rows = len(row_ptr) - 1
@@ -112,6 +124,36 @@ def bsr_spmm_bf16(brp, bci, bv_bits, B_bits, bs: int):
     lib().oracle_bsr_spmm_bf16(_I64(rows), _I64(bs), _I64(n), _ptr(brp), _ptr(bci), _ptr(bv_bits), _ptr(B_bits),
                                _ptr(out), _ptr(out32))
     return out, out32
+
+
+def bsr_abs_bound_bf16(brp, bci, bv_bits, B_bits, bs: int) -> np.ndarray:
+    """Per output of a bf16 BSR SpMM: the sum of |a * b| over its terms, f64."""
+    brp, bci, bv_bits, B_bits = _i32(brp), _i32(bci), _u16(bv_bits), _u16(B_bits)
+    rows, n = (len(brp) - 1) * bs, B_bits.shape[1]
+    out = np.empty((rows, n), dtype=np.float64)
+    lib().oracle_bsr_abs_bound_bf16(_I64(rows), _I64(bs), _I64(n), _ptr(brp), _ptr(bci), _ptr(bv_bits), _ptr(B_bits),
+                                    _ptr(out))
+    return out
+
+
+def bf16_mismatches(got_bits, want_bits, want_f32, bound) -> tuple[int, int]:
+    """Compares bf16 outputs (bit patterns) with the oracle's: (outputs further than one bf16 ulp from the
+    oracle's bits, counted where the exact sum is at least 2**-6 of the size of its terms; outputs of
+    cancelling sums, |sum| below that, whose error exceeds 1e-2 * 2**-6 of the size of their terms)."""
+    got = np.ascontiguousarray(got_bits).astype(np.uint16).ravel()
+    want = np.ascontiguousarray(want_bits).astype(np.uint16).ravel()
+    f32 = np.ascontiguousarray(want_f32, dtype=np.float32).ravel()
+    S = np.ascontiguousarray(bound, dtype=np.float64).ravel()
+
+    def ordered(bits):  # bf16 bit patterns -> integers in value order
+        b = bits.astype(np.int32)
+        return np.where(b & 0x8000, -(b & 0x7FFF), b)
+
+    regular = np.abs(f32) >= S * 2.0 ** -6
+    ulps = np.abs(ordered(got) - ordered(want))
+    got_f32 = (got.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    tiny_bad = (~regular) & (np.abs(got_f32 - f32) > 1e-2 * 2.0 ** -6 * S + 1e-30)
+    return int(np.sum(regular & (ulps > 1))), int(np.sum(tiny_bad))
 
 
 def partition(lower, upper, worker, count):

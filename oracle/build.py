@@ -24,8 +24,13 @@ REF_FLAGS = ["-O2", "-ffp-contract=off", "-std=c++17", "-shared", "-fPIC"]
 
 
 def reference_root() -> Path | None:
-    root = Path(os.environ.get("SPARSEWAVE_REFERENCE", "/root/reference"))
-    return root if (root / "benchmark" / "SparseBenchmarkUtils.cpp").exists() else None
+    """The SparseWave source tree: $SPARSEWAVE_REFERENCE, else a `reference` directory beside this
+    repository; None when neither holds the helper's source (the reference build is then skipped)."""
+    named = os.environ.get("SPARSEWAVE_REFERENCE")
+    for root in ([Path(named)] if named else []) + [HERE.parent.parent / "reference"]:
+        if (root / "benchmark" / "SparseBenchmarkUtils.cpp").exists():
+            return root
+    return None
 
 
 def _stale(target: Path, deps: list[Path]) -> bool:

@@ -82,6 +82,17 @@ ORACLE_API int oracle_num_threads(void) {
 #endif
 }
 
+/* Thread count of the OpenMP loops above.  Launchers that start one process per GPU export
+ * OMP_NUM_THREADS=1 to every rank; the timed CPU baseline sets the count it wants (the cores
+ * the process may run on) explicitly instead of inheriting that. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* Per-output tolerance scale: sum_p |val[p] * B[col[p], j]| in f64. */
 ORACLE_API void oracle_csr_abs_bound(int64_t rows, int64_t n, const int32_t *row_ptr,
                                      const int32_t *col, const float *val,
@@ -152,6 +163,29 @@ ORACLE_API void oracle_bsr_spmm_bf16(int64_t rows, int64_t bs, int64_t n,
       }
       C[r * n + j] = f32_to_bf16(sum);
       if (C_f32) C_f32[r * n + j] = sum;
+    }
+  }
+}
+
+/* Size of what a bf16 BSR output is summed from: sum over the row's terms of
+ * |a * b| in f64.  The bf16 tolerance of the tests is stated against it (an
+ * output much smaller than this sum comes from cancellation). */
+ORACLE_API void oracle_bsr_abs_bound_bf16(int64_t rows, int64_t bs, int64_t n,
+                                          const int32_t *brp, const int32_t *bci,
+                                          const uint16_t *bv, const uint16_t *B,
+                                          double *bound) {
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t r = 0; r < rows; ++r) {
+    const int64_t br = r / bs, lr = r % bs;
+    for (int64_t j = 0; j < n; ++j) {
+      double sum = 0.0;
+      for (int32_t bp = brp[br]; bp < brp[br + 1]; ++bp) {
+        const uint16_t *a = bv + ((int64_t)bp * bs + lr) * bs;
+        const uint16_t *b = B + ((int64_t)bci[bp] * bs) * n + j;
+        for (int64_t lc = 0; lc < bs; ++lc)
+          sum += fabs((double)bf16_to_f32(a[lc]) * (double)bf16_to_f32(b[lc * n]));
+      }
+      bound[r * n + j] = sum;
     }
   }
 }

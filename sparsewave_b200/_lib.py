@@ -81,6 +81,7 @@ SIGNATURES = {
     "swb_bsr_spmm_f32": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_bf16": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "swb_bsr16_spmm_bf16_static": (C.c_int, [_I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(C.c_int32)]),
+    "swb_bsr16_static_status": (C.c_int, [_P, C.POINTER(C.c_int32)]),
     "swb_spmv_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "swb_spmm_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "swb_bsr_spmm_bf16_host": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
@@ -88,6 +89,12 @@ SIGNATURES = {
     "swb_csr_release": (None, [_CTX, _P]),
     "swb_spmv_resident_host": (C.c_int, [_CTX, _OPT, _P, _P, _P]),
     "swb_spmm_resident_host": (C.c_int, [_CTX, _OPT, _P, _I64, _P, _P]),
+    "swb_probe_stream_gather": (C.c_int, [_CTX, _I64, _P, _P, _P, _P, _P]),
+    "swb_spmv_sharded": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
+    "swb_spmm_sharded": (C.c_int, [_CTX, _OPT, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
+    "swb_csr_upload_rows": (C.c_int, [_CTX, _I64, _I64, _P, _P, _P, _I64, _I64, C.POINTER(C.c_void_p)]),
+    "swb_spmv_sharded_host": (C.c_int, [_CTX, _OPT, _P, _P, _P]),
+    "swb_spmm_sharded_host": (C.c_int, [_CTX, _OPT, _P, _I64, _P, _P]),
     "swb_check_csr_host": (C.c_int, [_CTX, _I64, _I64, _I64, _P, _P]),
     "swb_spmv_memref": (C.c_int, [_CTX, _OPT, _P, _P, _P, _P, _P, _P]),
     "swb_spmm_memref": (C.c_int, [_CTX, _OPT, _P, _P, _P, _P, _P, _P]),

@@ -210,6 +210,44 @@ class Context:
             _dev_ptr(y, torch.float32, "y"), self._stream()))
         return y
 
+    def spmv_sharded(self, options, row_ptr, col_idx, val, x_owned, cols: int, y=None, *, rows=None):
+        """Row shard of y = A @ x: gathers every rank's chunk of x (this rank's is `x_owned`), then runs the
+        shard's kernel; collective over the context's communicator."""
+        rows = int(row_ptr.numel() - 1 if rows is None else rows)
+        if y is None:
+            y = torch.empty(rows, dtype=torch.float32, device=val.device)
+        o = self._opts(options)
+        self._check(self._lib.swb_spmv_sharded(
+            self._ctx, C.byref(o), rows, int(cols), int(val.numel()),
+            _dev_ptr(row_ptr, torch.int32, "row_ptr"), _dev_ptr(col_idx, torch.int32, "col_idx"),
+            _dev_ptr(val, torch.float32, "val"), _dev_ptr(x_owned, torch.float32, "x_owned"),
+            _dev_ptr(y, torch.float32, "y"), self._stream()))
+        return y
+
+    def spmm_sharded(self, options, row_ptr, col_idx, val, B_owned, cols: int, C_out=None, *, rows=None):
+        """Row shard of C = A @ B (see spmv_sharded); B_owned is this rank's rows of B."""
+        rows = int(row_ptr.numel() - 1 if rows is None else rows)
+        n_rhs = int(B_owned.shape[1])
+        if C_out is None:
+            C_out = torch.empty((rows, n_rhs), dtype=torch.float32, device=val.device)
+        o = self._opts(options)
+        self._check(self._lib.swb_spmm_sharded(
+            self._ctx, C.byref(o), rows, int(cols), int(val.numel()), n_rhs,
+            _dev_ptr(row_ptr, torch.int32, "row_ptr"), _dev_ptr(col_idx, torch.int32, "col_idx"),
+            _dev_ptr(val, torch.float32, "val"), _dev_ptr(B_owned, torch.float32, "B_owned"),
+            _dev_ptr(C_out, torch.float32, "C"), self._stream()))
+        return C_out
+
+    def probe_stream_gather(self, col_idx, val, x, sink=None):
+        """Roofline probe: the col/val streams and the gather of x with no row logic (swb_probe_stream_gather)."""
+        if sink is None:
+            sink = torch.zeros(1024, dtype=torch.float32, device=x.device)
+        self._check(self._lib.swb_probe_stream_gather(
+            self._ctx, int(val.numel()), _dev_ptr(col_idx, torch.int32, "col_idx"),
+            _dev_ptr(val, torch.float32, "val"), _dev_ptr(x, torch.float32, "x"),
+            _dev_ptr(sink, torch.float32, "sink"), self._stream()))
+        return sink
+
     def coo_spmv(self, options, rows: int, row_idx, col_idx, val, x, y=None):
         """y = A @ x for COO A (entries in any order, duplicates accumulate)."""
         cols, nnz = int(x.numel()), int(val.numel())
@@ -319,6 +357,17 @@ class Context:
                                              _host_ptr(val, torch.float32, "val"), C.byref(h)))
         return ResidentCsr(self, h, int(rows), int(cols))
 
+    def csr_upload_rows(self, cols: int, row_ptr, col_idx, val, row_begin: int, row_end: int) -> "ResidentCsr":
+        """Keeps rows [row_begin, row_end) of a host CSR matrix on the device (offsets rebased): the shard
+        of a rank, for the `*_sharded_host` calls."""
+        h = C.c_void_p()
+        self._check(self._lib.swb_csr_upload_rows(self._ctx, len(row_ptr) - 1, int(cols),
+                                                  _host_ptr(row_ptr, torch.int32, "row_ptr"),
+                                                  _host_ptr(col_idx, torch.int32, "col_idx"),
+                                                  _host_ptr(val, torch.float32, "val"), int(row_begin), int(row_end),
+                                                  C.byref(h)))
+        return ResidentCsr(self, h, int(row_end - row_begin), int(cols))
+
     def check_csr_host(self, rows, cols, row_ptr, col_idx) -> None:
         self._check(self._lib.swb_check_csr_host(self._ctx, rows, cols, len(col_idx),
                                                  _host_ptr(row_ptr, torch.int32, "row_ptr"),
@@ -343,6 +392,21 @@ class ResidentCsr:
         self.ctx._check(self.ctx._lib.swb_spmm_resident_host(self.ctx._ctx, C.byref(o), self._h, int(B.shape[1]),
                                                              _host_ptr(B, torch.float32, "B"),
                                                              _host_ptr(C_out, torch.float32, "C")))
+        return C_out
+
+    def spmv_sharded_host(self, options, x_owned, y):
+        """This rank's chunk of x in, the exchange and the shard's kernel on the device, this rank's rows out."""
+        o = self.ctx._opts(options)
+        self.ctx._check(self.ctx._lib.swb_spmv_sharded_host(self.ctx._ctx, C.byref(o), self._h,
+                                                            _host_ptr(x_owned, torch.float32, "x_owned"),
+                                                            _host_ptr(y, torch.float32, "y")))
+        return y
+
+    def spmm_sharded_host(self, options, B_owned, C_out):
+        o = self.ctx._opts(options)
+        self.ctx._check(self.ctx._lib.swb_spmm_sharded_host(self.ctx._ctx, C.byref(o), self._h, int(B_owned.shape[1]),
+                                                            _host_ptr(B_owned, torch.float32, "B_owned"),
+                                                            _host_ptr(C_out, torch.float32, "C")))
         return C_out
 
     def release(self) -> None:
@@ -370,6 +434,17 @@ def bsr16_spmm_bf16_static(block_row_ptr, block_col_idx, block_values, B, C_out=
     if wait and gave_up.value != 0:
         raise SparseWaveError(_lib.SWB_ERR_CUDA, f"{gave_up.value} CTAs abandoned a barrier wait")
     return C_out
+
+
+def bsr16_static_status() -> int:
+    """CTAs of the most recent static call on the current device that abandoned a wait (synchronises the
+    current stream; allocates nothing)."""
+    lib = _lib.load()
+    gave_up = C.c_int32(-1)
+    st = lib.swb_bsr16_static_status(torch.cuda.current_stream().cuda_stream, C.byref(gave_up))
+    if st != 0:
+        raise SparseWaveError(st, lib.swb_last_error(None).decode())
+    return int(gave_up.value)
 
 
 # -- context-free helpers (host arithmetic only; need no GPU) ---------------------------

@@ -46,7 +46,8 @@ __global__ void bsr_spmm_thread_per_output_kernel(int64_t rows, int64_t N, int64
 
 cudaError_t launch_bsr_spmm_thread_per_output_f32(const BsrSpmmArgs &a, int block, cudaStream_t s,
                                                   int64_t *launches) {
-  const unsigned grid = (unsigned)max1(ceil_div(a.rows * a.n_rhs, block));
+  unsigned grid = 0;  // refused, not truncated, beyond the CUDA grid limit
+  if (!grid_dim(ceil_div(a.rows * a.n_rhs, block), &grid)) return cudaErrorInvalidConfiguration;
   bsr_spmm_thread_per_output_kernel<float><<<grid, block, 0, s>>>(
       a.rows, a.n_rhs, a.block_size, a.block_row_ptr, a.block_col_idx,
       static_cast<const float *>(a.block_values), static_cast<const float *>(a.B),
@@ -57,7 +58,8 @@ cudaError_t launch_bsr_spmm_thread_per_output_f32(const BsrSpmmArgs &a, int bloc
 
 cudaError_t launch_bsr_spmm_thread_per_output_bf16(const BsrSpmmArgs &a, int block, cudaStream_t s,
                                                    int64_t *launches) {
-  const unsigned grid = (unsigned)max1(ceil_div(a.rows * a.n_rhs, block));
+  unsigned grid = 0;  // refused, not truncated, beyond the CUDA grid limit
+  if (!grid_dim(ceil_div(a.rows * a.n_rhs, block), &grid)) return cudaErrorInvalidConfiguration;
   bsr_spmm_thread_per_output_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(
       a.rows, a.n_rhs, a.block_size, a.block_row_ptr, a.block_col_idx,
       static_cast<const __nv_bfloat16 *>(a.block_values), static_cast<const __nv_bfloat16 *>(a.B),

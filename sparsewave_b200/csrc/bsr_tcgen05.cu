@@ -37,6 +37,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "swb_index.h"
@@ -288,14 +289,15 @@ bool bsr16_tcgen05_supported(const BsrSpmmArgs &a) {
 cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, const DeviceInfo &dev,
                                       cudaStream_t s, int64_t *launches) {
   (void)dev;
-  static bool configured[64] = {};
+  // Once per device; racing host threads at worst repeat the (idempotent) attribute call.
+  static std::atomic<bool> configured[64];
   int device = 0;
   cudaGetDevice(&device);
-  if (device < 0 || device >= 64 || !configured[device]) {
+  if (device < 0 || device >= 64 || !configured[device].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(bsr16_spmm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    if (device >= 0 && device < 64) configured[device] = true;
+    if (device >= 0 && device < 64) configured[device].store(true, std::memory_order_release);
   }
   const int64_t brows = a.rows / 16;
   if (brows == 0) return cudaSuccess;
@@ -348,8 +350,16 @@ static __device__ __align__(256) int swb_static_status_words[SWB_STATIC_MAX_CTAS
 // In host code `swb_static_status_words` is only a handle for the symbol, not a
 // device address; the address a kernel can use comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
-int *static_status_address(cudaError_t *err) {
-  static int *address[64] = {};
+// Host-side record per device: the array's device address and the number of words the most recent call
+// on that device used.  Atomics, so that host threads may call concurrently (two threads that both find
+// the address missing ask for it twice and store the same value).
+struct StaticStatusSlot {
+  std::atomic<int *> address{nullptr};
+  std::atomic<int64_t> last_grid{0};
+};
+StaticStatusSlot g_static_slots[64];
+
+int *static_status_address(cudaError_t *err, StaticStatusSlot **slot_out = nullptr) {
   int device = 0;
   *err = cudaGetDevice(&device);
   if (*err != cudaSuccess) return nullptr;
@@ -357,13 +367,32 @@ int *static_status_address(cudaError_t *err) {
     *err = cudaErrorInvalidDevice;
     return nullptr;
   }
-  if (!address[device]) {
+  StaticStatusSlot &slot = g_static_slots[device];
+  if (slot_out) *slot_out = &slot;
+  int *address = slot.address.load(std::memory_order_acquire);
+  if (!address) {
     void *p = nullptr;
     *err = cudaGetSymbolAddress(&p, swb_static_status_words);
     if (*err != cudaSuccess) return nullptr;
-    address[device] = static_cast<int *>(p);
+    address = static_cast<int *>(p);
+    slot.address.store(address, std::memory_order_release);
   }
-  return address[device];
+  return address;
+}
+
+// Counts the non-zero words among the first `grid` through pageable stack memory: no pinned or device
+// allocation.  The stream must be idle.
+cudaError_t count_status_words(const int *status, int64_t grid, int32_t *count_out) {
+  int32_t count = 0;
+  int piece[1024];
+  for (int64_t off = 0; off < grid; off += 1024) {
+    const int64_t n = grid - off < 1024 ? grid - off : 1024;
+    cudaError_t e = cudaMemcpy(piece, status + off, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    for (int64_t i = 0; i < n; ++i) count += piece[i] != 0;
+  }
+  *count_out = count;
+  return cudaSuccess;
 }
 
 int static_fail(int status, const char *fmt, long long a = 0, long long b = 0) {
@@ -409,7 +438,8 @@ extern "C" __attribute__((visibility("default"))) int swb_bsr16_spmm_bf16_static
   if (grid == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaSuccess;
-  int *status = static_status_address(&e);
+  StaticStatusSlot *slot = nullptr;
+  int *status = static_status_address(&e, &slot);
   if (!status) return static_fail(kCuda, cudaGetErrorString(e));
   e = cudaFuncSetAttribute(bsr16_spmm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
@@ -424,20 +454,29 @@ extern "C" __attribute__((visibility("default"))) int swb_bsr16_spmm_bf16_static
       map_B, map_A, n_tiles, n_rhs, block_row_ptr, block_col_idx, reinterpret_cast<__nv_bfloat16 *>(C), status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
+  slot->last_grid.store(grid, std::memory_order_release);
   if (gave_up_ctas) {
-    // Host copy of the status words through pageable memory on the stack, in
-    // pieces: no pinned or device allocation.
     e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess) e = count_status_words(status, grid, gave_up_ctas);
     if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
-    int32_t count = 0;
-    int piece[1024];
-    for (int64_t off = 0; off < grid; off += 1024) {
-      const int64_t n = grid - off < 1024 ? grid - off : 1024;
-      e = cudaMemcpy(piece, status + off, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost);
-      if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
-      for (int64_t i = 0; i < n; ++i) count += piece[i] != 0;
-    }
-    *gave_up_ctas = count;
   }
+  return 0;
+}
+
+// Outcome of the most recent swb_bsr16_spmm_bf16_static call on the current device, for callers that
+// passed gave_up_ctas == NULL: waits for `stream` and counts the CTAs of that call whose bounded wait
+// gave up.  Allocates nothing.
+extern "C" __attribute__((visibility("default"))) int swb_bsr16_static_status(void *stream, int32_t *gave_up_ctas) {
+  using namespace swb;
+  constexpr int kInvalidArgument = -3, kCuda = -4;
+  if (!gave_up_ctas) return static_fail(kInvalidArgument, "bsr16 static status: gave_up_ctas is NULL");
+  *gave_up_ctas = 0;
+  cudaError_t e = cudaSuccess;
+  StaticStatusSlot *slot = nullptr;
+  int *status = static_status_address(&e, &slot);
+  if (!status) return static_fail(kCuda, cudaGetErrorString(e));
+  e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = count_status_words(status, slot->last_grid.load(std::memory_order_acquire), gave_up_ctas);
+  if (e != cudaSuccess) return static_fail(kCuda, cudaGetErrorString(e));
   return 0;
 }

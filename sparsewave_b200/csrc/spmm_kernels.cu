@@ -379,11 +379,16 @@ __global__ void spmm_thread_per_position_kernel(int64_t rows, int64_t nnz, int64
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// CUDA grids hold at most 2^31 - 1 blocks in x; a launch that needs more is refused instead of truncated.
+#define SWB_GRID(name, blocks)                                      \
+  unsigned name = 0;                                                 \
+  if (!grid_dim(blocks, &name)) return cudaErrorInvalidConfiguration
+
 template <int TCAP>
 cudaError_t launch_tile(const CsrSpmmArgs &a, int block, int T, cudaStream_t s) {
   const int64_t tiles = ceil_div(a.n_rhs, T);
   const int64_t units = a.rows * tiles;
-  const unsigned grid = (unsigned)max1(ceil_div(units, block / 32));
+  SWB_GRID(grid, ceil_div(units, block / 32));
   const bool vec = (T == TCAP) && (TCAP % 4 == 0) && (a.n_rhs % 4 == 0) && (a.n_rhs % T == 0) &&
                    aligned16(a.B) && aligned16(a.C);
   if (vec) {
@@ -400,7 +405,8 @@ cudaError_t launch_tile(const CsrSpmmArgs &a, int block, int T, cudaStream_t s) 
 template <int G, int L>
 cudaError_t launch_subwarp(const CsrSpmmArgs &a, int block, cudaStream_t s) {
   const int64_t warps = ceil_div(a.rows, 32 / L);
-  spmm_subwarp_row_kernel<G, L><<<(unsigned)max1(ceil_div(warps, block / 32)), block, 0, s>>>(
+  SWB_GRID(grid, ceil_div(warps, block / 32));
+  spmm_subwarp_row_kernel<G, L><<<grid, block, 0, s>>>(
       a.rows, a.n_rhs, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
   return cudaGetLastError();
 }
@@ -422,7 +428,7 @@ cudaError_t launch_row_of_tiles(const CsrSpmmArgs &a, int block, cudaStream_t s)
 
 cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block, cudaStream_t s,
                                           int64_t *launches) {
-  const unsigned grid = (unsigned)max1(ceil_div(a.rows * a.n_rhs, block));
+  SWB_GRID(grid, ceil_div(a.rows * a.n_rhs, block));
   spmm_thread_per_output_kernel<<<grid, block, 0, s>>>(a.rows, a.n_rhs, a.row_ptr, a.col_idx,
                                                        a.val, a.B, a.C);
   ++*launches;
@@ -442,7 +448,7 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
     if (N == 8) return launch_row_of_tiles<2>(a, block, s);
     if (N == 16) return launch_row_of_tiles<4>(a, block, s);
     if (N == 32) return launch_row_of_tiles<8>(a, block, s);
-    const unsigned grid = (unsigned)max1(ceil_div(a.rows, block / 32));
+    SWB_GRID(grid, ceil_div(a.rows, block / 32));
     if (N == 64)
       spmm_wave_per_row_fused_kernel<16><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,
                                                                  a.accumulate);
@@ -474,12 +480,12 @@ int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs
 cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block, int64_t chunk,
                                             cudaStream_t s, int64_t *launches) {
   // Zero fill of the flattened output, then the atomic schedule.
+  const int64_t workers = ceil_div(a.nnz * a.n_rhs, chunk);
+  SWB_GRID(grid, ceil_div(workers, block));
   if (!a.accumulate) {
     cudaError_t e = launch_fill_zero(a.C, a.rows * a.n_rhs, block, s, launches);
     if (e != cudaSuccess) return e;
   }
-  const int64_t workers = ceil_div(a.nnz * a.n_rhs, chunk);
-  const unsigned grid = (unsigned)max1(ceil_div(workers, block));
   spmm_thread_per_position_kernel<<<grid, block, 0, s>>>(a.rows, a.nnz, a.n_rhs, chunk, a.row_ptr,
                                                          a.col_idx, a.val, a.B, a.C);
   ++*launches;

@@ -6,6 +6,8 @@
 // arith.mulf + arith.addf (SparseWaveToGPU.cpp:252-256).  thread-per-row adds
 // in position order, so it reproduces the CPU CSR loop bit for bit; the
 // cooperative mappings add the same products in a tree order.
+#include <atomic>
+
 #include "swb_index.h"
 #include "swb_kernels.h"
 
@@ -17,17 +19,49 @@ constexpr unsigned FULL = 0xffffffffu;
 __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
 __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
 
-// Streaming loads for data read once (col/val), cached loads for x.
+// L2 eviction priorities per instruction: the col/val streams of the vectorised kernels are marked
+// evict-first and the gathered vector evict-last, so that a stream far larger than L2 does not push the
+// vector's lines out (measured on a 92 M-nonzero SpMV: 1.39x the algorithmic DRAM bytes without the
+// hints, 1.01x with them).  No device-wide setting is involved.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// Streaming loads for data read once (col/val).
 __device__ __forceinline__ int ld_stream(const int32_t *p) { return __ldcs(p); }
 __device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
-__device__ __forceinline__ int4 ld_stream(const int4 *p) { return __ldcs(p); }
-__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ int4 ld_stream(const int4 *p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.s32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(l2_policy_evict_first()));
+  return v;
+}
+__device__ __forceinline__ float4 ld_stream(const float4 *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(l2_policy_evict_first()));
+  return v;
+}
 
-// Gather of one x element: read-only path, no L1 allocation (the 13 % L1 hit
-// rate of a random gather does not pay for the fills).
+// Gather of one x element: read-only path, no L1 allocation (the 13 % L1 hit rate of a random gather
+// does not pay for the fills), kept in L2.
 __device__ __forceinline__ float ld_x(const float *p) {
   float v;
-  asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.f32 %0, [%1], %2;"
+               : "=f"(v) : "l"(p), "l"(l2_policy_evict_last()));
+  return v;
+}
+__device__ __forceinline__ float4 ld_x4(const float4 *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(l2_policy_evict_last()));
   return v;
 }
 
@@ -613,12 +647,44 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_per_position_kernel(int64
 }
 
 #include "spmv_wave_span.cuh"
+#include "spmv_band.cuh"
+
+// ---------------------------------------------------------------------------
+// Roofline probe: the col/val streams and the gather of x with no row logic at all (every warp adds its
+// products into one of 1024 sinks).  What this kernel takes on a matrix's own arrays is the floor of any
+// SpMV mapping that reads x[col[p]] through the cache hierarchy: on a vector much larger than L1 the
+// rate of 32-byte sector requests, not HBM, sets it.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) stream_gather_probe_kernel(const int4 *__restrict__ col4,
+                                                                  const float4 *__restrict__ val4,
+                                                                  const float *__restrict__ x, int64_t n4,
+                                                                  float *__restrict__ sink) {
+  float s = 0.0f;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const int4 c = ld_stream(col4 + i);
+    const float4 v = ld_stream(val4 + i);
+    const float x0 = ld_x(x + c.x), x1 = ld_x(x + c.y), x2 = ld_x(x + c.z), x3 = ld_x(x + c.w);
+    s = add(s, add(add(mul(v.x, x0), mul(v.y, x1)), add(mul(v.z, x2), mul(v.w, x3))));
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) atomicAdd(sink + (blockIdx.x & 1023), s);
+}
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline unsigned grid_of(int64_t blocks) { return (unsigned)max1(blocks); }
 
 }  // namespace
+
+cudaError_t launch_stream_gather_probe(int64_t nnz, const int32_t *col, const float *val, const float *x, float *sink,
+                                       const DeviceInfo &dev, cudaStream_t s, int64_t *launches) {
+  if (!aligned16(col) || !aligned16(val)) return cudaErrorMisalignedAddress;
+  stream_gather_probe_kernel<<<(unsigned)(dev.sm_count * 16), 256, 0, s>>>(
+      reinterpret_cast<const int4 *>(col), reinterpret_cast<const float4 *>(val), x, nnz / 4, sink);
+  ++*launches;
+  return cudaGetLastError();
+}
 
 cudaError_t launch_fill_zero(float *y, int64_t n, int block, cudaStream_t s, int64_t *launches) {
   // Thread mapping over len(y) (SparsePositionScheduling.cpp:31-47); the grid
@@ -716,28 +782,78 @@ int64_t wave_per_position_physical_grid(int64_t nnz, int block, int64_t batch) {
   return max1(ceil_div(spans, block / 32));
 }
 
+// Shape of the long-row path for a matrix, or false when the span kernel alone is used: small problems
+// (the three extra launches would cost more than they save), more bands than a grid dimension holds, or
+// operands without the 16-byte alignment of the 128-bit loads.
+bool band_path_plan(const CsrSpmvArgs &a, int64_t min_nnz, BandPlan *plan) {
+  if (a.nnz < min_nnz || a.nnz < 1 || a.cols < 1) return false;
+  const int64_t bands = ceil_div(a.cols, BAND_COLS);
+  if (bands > 4096) return false;
+  if (!aligned16(a.col_idx) || !aligned16(a.val) || !aligned16(a.x)) return false;
+  plan->bands = (int)bands;
+  plan->long_min = (int)(32 * bands < 256 ? 256 : 32 * bands);
+  plan->cap = (int)(a.nnz / plan->long_min) + 1;
+  return true;
+}
+
+size_t band_scratch_bytes(const BandPlan &plan) {
+  // counter (padded), list of long rows, (bands + 1) x cap table of run starts
+  return 256 + (size_t)plan.cap * 4 + (size_t)(plan.bands + 1) * (size_t)plan.cap * 4;
+}
+
 cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64_t batch,
                                           const PositionTrace &trace, cudaStream_t s,
-                                          int64_t *launches, int64_t *physical_grid) {
-  if (!a.accumulate) {
-    cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
-    if (e != cudaSuccess) return e;
-  }
+                                          int64_t *launches, int64_t *physical_grid,
+                                          const BandPlan *band, void *band_scratch, const DeviceInfo &dev) {
   const int64_t waves = wave_position_wave_count(a.nnz, block);
   const int64_t grid = wave_per_position_physical_grid(a.nnz, block, batch);
   if (physical_grid) *physical_grid = grid;
-  const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
   // Spans of two or more partitions take the chunked span kernel (needs
   // 16-byte aligned col/val); batch == 1 is the reference schedule, one
   // partition per warp and lane == position.  Blocks above 512 threads need
   // the register-capped instantiation.
   const bool span = batch >= 2 && aligned16(a.col_idx) && aligned16(a.val);
+  const bool banded = span && band && band_scratch && !trace.enabled();
+  int long_min = 0;
+  int *count = nullptr, *long_rows = nullptr, *tab = nullptr;
+  if (banded) {
+    // zero fill fused with the search for long rows, then the band boundaries of those rows
+    static std::atomic<bool> configured[64];
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64 || !configured[device].load(std::memory_order_acquire)) {
+      cudaError_t e = cudaFuncSetAttribute(spmv_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)BAND_SMEM);
+      if (e != cudaSuccess) return e;
+      if (device >= 0 && device < 64) configured[device].store(true, std::memory_order_release);
+    }
+    long_min = band->long_min;
+    count = static_cast<int *>(band_scratch);
+    long_rows = count + 64;
+    tab = long_rows + band->cap;
+    cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int), s);
+    if (e != cudaSuccess) return e;
+    int64_t blocks = max1(ceil_div(a.rows, 256));
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    find_long_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>(a.y, a.rows, !a.accumulate, a.row_ptr, long_min, band->cap,
+                                                          count, long_rows);
+    ++*launches;
+    band_bounds_kernel<<<(unsigned)(band->cap < 148 * 64 ? band->cap : 148 * 64), 128, 0, s>>>(
+        a.row_ptr, a.col_idx, band->bands, band->cap, count, long_rows, tab);
+    ++*launches;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  } else if (!a.accumulate) {
+    cudaError_t e = launch_fill_zero(a.y, a.rows, block, s, launches);
+    if (e != cudaSuccess) return e;
+  }
+  const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
   const size_t span_smem = (size_t)(block / 32) * SPAN_CHUNK * sizeof(int);
 #define SWB_WPP(TR, MB)                                                                   \
   do {                                                                                    \
     if (span)                                                                             \
       spmv_wave_span_kernel<TR, MB><<<(unsigned)grid, block, span_smem, s>>>(              \
-          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);      \
+          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace, long_min); \
     else                                                                                  \
       spmv_wave_per_position_kernel<TR, MB><<<(unsigned)grid, block, smem, s>>>(           \
           a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);      \
@@ -748,6 +864,11 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
     if (block > 512) SWB_WPP(false, 1024); else SWB_WPP(false, 512);
   }
 #undef SWB_WPP
+  ++*launches;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || !banded) return e;
+  spmv_band_kernel<<<(unsigned)dev.sm_count, BAND_THREADS, BAND_SMEM, s>>>(
+      a.nnz, a.cols, a.col_idx, a.val, a.x, a.y, band->bands, band->cap, count, long_rows, tab);
   ++*launches;
   return cudaGetLastError();
 }

@@ -27,6 +27,12 @@
 // SparseGPUUtils.cpp:247-292); a lane's first run closes with the scanned value
 // of the lane below.  One atomicAdd per (row, span) segment; the segment still
 // open at the end of a chunk is carried in registers.
+//
+// long_min > 0: rows of at least long_min (>= 256) positions belong to the band kernel
+// (spmv_band.cuh) and are left out here.  A row that long is never inside one chunk, so only the row that
+// enters a chunk and the row that leaves it can be long: chunks that lie wholly in such a row are jumped
+// over without a load, and in a chunk with row boundaries their positions count as zero (the reduction
+// then adds 0.0f to that row, which changes nothing).
 #pragma once
 
 constexpr int SPAN_CHUNK = 128;
@@ -49,7 +55,7 @@ template <bool TRACE, int MAX_BLOCK>
 __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
     int64_t rows, int64_t nnz, int64_t wave_count, int64_t batch, const int32_t *__restrict__ row_ptr,
     const int32_t *__restrict__ col, const float *__restrict__ val, const float *__restrict__ x,
-    float *__restrict__ y, PositionTrace trace) {
+    float *__restrict__ y, PositionTrace trace, int long_min) {
   extern __shared__ int smem_rows[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -76,6 +82,9 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
 
   int R = warp_row_search(row_ptr, (int)rows + 1, sb, lane);
   int next_b = __ldg(row_ptr + R + 1);  // first position of the next non-empty row (or nnz)
+  // the row that enters the current chunk belongs to the band kernel
+  bool head_long = long_min > 0 && next_b - __ldg(row_ptr + R) >= long_min;
+  if (head_long && next_b >= se) return;  // the whole span lies inside a long row
   int carry_row = -1;
   float acc = 0.0f;
   int carry_last = sb;
@@ -104,6 +113,14 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
 
   for (int cb = sb & ~3; cb < se; cb += SPAN_CHUNK) {
     const int ce = (cb + SPAN_CHUNK < se) ? cb + SPAN_CHUNK : se;
+    if (head_long && next_b >= ce) {
+      // The chunk lies in a long row: go on at the chunk that holds the row's end (or stop).
+      if (next_b >= se) break;
+      const int skip = (next_b - cb) / SPAN_CHUNK;  // >= 1 whole chunks to leave out, this one included
+      cb += (skip - 1) * SPAN_CHUNK;
+      load_chunk(cb + SPAN_CHUNK, cn, vn);  // the chunk the loop goes on with
+      continue;
+    }
     const int p0 = cb + 4 * lane;
     const int4 c = cn;
     const float4 v = vn;
@@ -168,9 +185,23 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
       if (m3) { trace.row_of_position[p0 + 3] = r3; trace.worker_of_position[p0 + 3] = wave_of(p0 + 3); }
     }
 
+    // ---- positions of long rows count as zero here (the band kernel adds them) ----------
+    float z0 = q0, z1 = q1, z2 = q2, z3 = q3;
+    bool tail_long = false;
+    if (long_min > 0) {
+      tail_long = __ldg(row_ptr + R_last + 1) - __ldg(row_ptr + R_last) >= long_min;
+      if (head_long || tail_long) {
+        const int ra = head_long ? R : -1, rb = tail_long ? R_last : -1;
+        if (r0 == ra || r0 == rb) z0 = 0.0f;
+        if (r1 == ra || r1 == rb) z1 = 0.0f;
+        if (r2 == ra || r2 == rb) z2 = 0.0f;
+        if (r3 == ra || r3 == rb) z3 = 0.0f;
+      }
+    }
+
     // ---- runs inside the lane --------------------------------------------------
     const int head_row = r0;
-    float head = q0, cur = q0;
+    float head = z0, cur = z0;
     int cur_row = r0;
     bool in_head = true;
     int head_last = p0 + 3;  // last position of the head run
@@ -183,9 +214,9 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
       cur_row = (RJ);                                          \
       cur = (QJ);                                              \
     }
-    SWB_RUN_STEP(r1, q1, 1)
-    SWB_RUN_STEP(r2, q2, 2)
-    SWB_RUN_STEP(r3, q3, 3)
+    SWB_RUN_STEP(r1, z1, 1)
+    SWB_RUN_STEP(r2, z2, 2)
+    SWB_RUN_STEP(r3, z3, 3)
 #undef SWB_RUN_STEP
     const bool single = in_head;
     const int tail_row = cur_row;
@@ -230,6 +261,7 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
     carry_last = ce - 1;
     R = R_last;
     next_b = __ldg(row_ptr + R + 1);
+    head_long = tail_long;
   }
   if (carry_row >= 0) {
     const float total = warp_sum(acc);

@@ -31,7 +31,15 @@ struct swb_context {
   // The dense operand of those calls travels here in two halves.
   cudaStream_t upload_stream = nullptr;
   cudaEvent_t upload_done[2] = {};
+  // Scratch of the long-row path of wave-per-position SpMV (list of long rows and their band
+  // boundaries): grown on demand by the first call that needs it, kept.
+  void *band_scratch = nullptr;
+  size_t band_scratch_bytes = 0;
   int *status_flag = nullptr;  // device int for kernels with bounded waits
+  // Sharded operators: device copy of this rank's chunk of the dense operand padded to the common chunk
+  // size, and the gathered operand when no peer window serves (both grown on demand, kept).
+  char *shard_send = nullptr, *shard_full = nullptr;
+  size_t shard_send_bytes = 0, shard_full_bytes = 0;
   void *comm = nullptr;        // NCCL communicator of the multi-GPU path (swb_comm.cu)
   void *peer_window = nullptr; // peer-store all-gather window (swb_peer_window.cu)
   int comm_ranks = 1, comm_rank = 0;
@@ -191,6 +199,15 @@ int64_t env_i64(const char *name, int64_t fallback) {
   return (*end == '\0' && v > 0) ? v : fallback;
 }
 
+// like env_i64, but "0" is a value
+int64_t env_i64_or_zero(const char *name, int64_t fallback) {
+  const char *text = getenv(name);
+  if (!text || !*text) return fallback;
+  char *end = nullptr;
+  long long v = strtoll(text, &end, 10);
+  return (*end == '\0' && v >= 0) ? v : fallback;
+}
+
 #define SWB_CUDA(ctx, call)                                   \
   do {                                                        \
     cudaError_t e__ = (call);                                 \
@@ -243,9 +260,12 @@ int swb_device_status(swb_context *ctx, swb_stream stream, int32_t *status) {
 void swb_destroy(swb_context *ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
-  swb_comm_window_destroy(ctx);
+  swb::abandon_peer_window(ctx);  // never a collective here: the other ranks may be gone
   swb_comm_destroy(ctx);
   if (ctx->workspace) cudaFree(ctx->workspace);
+  if (ctx->band_scratch) cudaFree(ctx->band_scratch);
+  if (ctx->shard_send) cudaFree(ctx->shard_send);
+  if (ctx->shard_full) cudaFree(ctx->shard_full);
   if (ctx->status_flag) cudaFree(ctx->status_flag);
   if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
   if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
@@ -517,6 +537,10 @@ int swb_launch_shape_query(swb_context *ctx, const swb_options *o, int64_t rows,
     if (o->spmm_mapping == SWB_WAVE_PER_ROW_TILE)  // rows of B of 4 ... 128 floats: the tiles of a row are fused
       r.physical_grid = swb::wave_per_row_tile_physical_grid(rows, nnz, n_rhs, (int)B, (int)o->spmm_tile_size);
   }
+  if (r.physical_grid > swb::kMaxGridX)
+    return fail(ctx, SWB_ERR_UNSUPPORTED,
+                "the launch needs %lld blocks, more than a CUDA grid holds (%lld); use a larger block or tile size",
+                (long long)r.physical_grid, (long long)swb::kMaxGridX);
   *out = r;
   return SWB_OK;
 }
@@ -558,7 +582,27 @@ static int spmv_impl(swb_context *ctx, const swb_options *o, int64_t rows, int64
     case SWB_WAVE_PER_POSITION: {
       int64_t batch = o->wave_position_batch > 0 ? o->wave_position_batch
                                                  : swb::wave_per_position_auto_batch(nnz, B, ctx->dev);
-      e = swb::launch_spmv_wave_per_position(a, B, batch, trace, stream, &ctx->launches, nullptr);
+      // Automatic batch on a large matrix: long rows can go through shared-memory bands of x.  The scratch
+      // memory is allocated by the first call that needs it (make that call outside stream capture).
+      swb::BandPlan plan;
+      // Opt-in: SWB_BAND_MIN_NNZ = nonzeros from which the path is taken (unset or 0: never; on a 92 M-nonzero
+      // power-law matrix it is correct but 8 % slower than the span kernel alone).
+      const int64_t band_min_nnz = env_i64_or_zero("SWB_BAND_MIN_NNZ", 0);
+      const bool banded = o->wave_position_batch == 0 && !trace.enabled() && band_min_nnz > 0 &&
+                          swb::band_path_plan(a, band_min_nnz, &plan);
+      if (banded) {
+        const size_t need = swb::band_scratch_bytes(plan);
+        if (need > ctx->band_scratch_bytes) {
+          if (ctx->band_scratch) cudaFree(ctx->band_scratch);
+          ctx->band_scratch = nullptr;
+          ctx->band_scratch_bytes = 0;
+          cudaError_t me = cudaMalloc(&ctx->band_scratch, need);
+          if (me != cudaSuccess) return cuda_fail(ctx, me, "cudaMalloc(long-row scratch)");
+          ctx->band_scratch_bytes = need;
+        }
+      }
+      e = swb::launch_spmv_wave_per_position(a, B, batch, trace, stream, &ctx->launches, nullptr,
+                                             banded ? &plan : nullptr, banded ? ctx->band_scratch : nullptr, ctx->dev);
       break;
     }
   }
@@ -571,6 +615,20 @@ int swb_spmv(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
              swb_stream stream) {
   return spmv_impl(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, swb::PositionTrace(),
                    static_cast<cudaStream_t>(stream));
+}
+
+int swb_probe_stream_gather(swb_context *ctx, int64_t nnz, const int32_t *col_idx, const float *val, const float *x,
+                            float *sink, swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (nnz < 0 || !col_idx || !val || !x || !sink)
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "gather probe: NULL pointer or negative size");
+  cudaError_t e = swb::launch_stream_gather_probe(nnz, col_idx, val, x, sink, ctx->dev, static_cast<cudaStream_t>(stream),
+                                                  &ctx->launches);
+  if (e == cudaErrorMisalignedAddress)
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "gather probe: col_idx and val must be 16-byte aligned");
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "gather probe launch");
+  return SWB_OK;
 }
 
 int swb_coo_spmv(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
@@ -629,6 +687,9 @@ int swb_spmm(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL operand pointer");
   if (o->accumulate && o->spmm_mapping == SWB_THREAD_PER_OUTPUT)
     return fail(ctx, SWB_ERR_UNSUPPORTED, "accumulate is not available for the thread-per-output SpMM mapping");
+  swb_launch_shape shape;
+  st = swb_launch_shape_query(ctx, o, rows, nnz, n_rhs, &shape);  // refuses grids beyond the CUDA limit
+  if (st != SWB_OK) return st;
   swb::CsrSpmmArgs a{rows, cols, nnz, n_rhs, row_ptr, col_idx, val, B, C};
   a.accumulate = o->accumulate != 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -721,9 +782,20 @@ int swb_check_csr_host(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz
   return SWB_OK;
 }
 
+// The host-buffer calls treat the caller's result buffer as write-only (it is never copied to the
+// device), so there is nothing for `accumulate` to add to.
+static int reject_host_accumulate(swb_context *ctx, const swb_options *o) {
+  if (o && o->accumulate)
+    return fail(ctx, SWB_ERR_UNSUPPORTED,
+                "accumulate is not available for the host-buffer calls: their result buffer is write-only");
+  return SWB_OK;
+}
+
 int swb_spmv_host(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
                   const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x, float *y) {
-  int st = check_ctx(ctx);
+  int st = reject_host_accumulate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   st = check_csr_sizes(ctx, "spmv", rows, cols, nnz);
   if (st != SWB_OK) return st;
@@ -755,7 +827,9 @@ int swb_spmv_host(swb_context *ctx, const swb_options *o, int64_t rows, int64_t 
 
 int swb_spmm_host(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz, int64_t n_rhs,
                   const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *B, float *C) {
-  int st = check_ctx(ctx);
+  int st = reject_host_accumulate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   st = check_csr_sizes(ctx, "spmm", rows, cols, nnz);
   if (st != SWB_OK) return st;
@@ -934,8 +1008,9 @@ int swb_plan_row_panels(int64_t rows, int64_t nnz, const int32_t *row_ptr, int64
   return plan_panels(rows, nnz, row_ptr, panel_nnz, panel_rows);
 }
 
-int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, const int32_t *row_ptr,
-                   const int32_t *col_idx, const float *val, swb_csr_handle **out) {
+// `plain`: one copy of the matrix, no row panels and no column parts (the matrix of a sharded operator).
+static int csr_upload_impl(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, const int32_t *row_ptr,
+                           const int32_t *col_idx, const float *val, bool plain, swb_csr_handle **out) {
   int st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   if (!out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: out is NULL");
@@ -946,10 +1021,10 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
   swb_csr_handle *h = new swb_csr_handle();
   h->rows = rows; h->cols = cols; h->nnz = nnz;
   h->panel_min_bytes = env_i64("SWB_RESIDENT_PANEL_BYTES", 512 * 1024);
-  const int64_t panel_nnz = env_i64("SWB_RESIDENT_PANEL_NNZ", 20000000);
+  const int64_t panel_nnz = plain ? 0 : env_i64("SWB_RESIDENT_PANEL_NNZ", 20000000);
   cudaError_t e = upload_part(h->whole, rows, nnz, row_ptr, col_idx, val, panel_nnz);
 
-  if (e == cudaSuccess && rows > 0 && cols >= 2 && nnz >= env_i64("SWB_RESIDENT_SPLIT_NNZ", 40000000)) {
+  if (!plain && e == cudaSuccess && rows > 0 && cols >= 2 && nnz >= env_i64("SWB_RESIDENT_SPLIT_NNZ", 40000000)) {
     // The two column parts, each a CSR matrix over all rows with the entries in their original order.  They
     // are an optimisation: without the host or device memory for them the matrix stays resident uncut.
     // Where the columns are cut: the first part should finish computing about when the rest of the operand
@@ -1004,6 +1079,29 @@ int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, co
   }
   *out = h;
   return SWB_OK;
+}
+
+int swb_csr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnz, const int32_t *row_ptr,
+                   const int32_t *col_idx, const float *val, swb_csr_handle **out) {
+  return csr_upload_impl(ctx, rows, cols, nnz, row_ptr, col_idx, val, false, out);
+}
+
+int swb_csr_upload_rows(swb_context *ctx, int64_t rows_total, int64_t cols, const int32_t *row_ptr,
+                        const int32_t *col_idx, const float *val, int64_t row_begin, int64_t row_end,
+                        swb_csr_handle **out) {
+  if (!out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: out is NULL");
+  *out = nullptr;
+  if (!row_ptr || rows_total < 0 || row_begin < 0 || row_end < row_begin || row_end > rows_total)
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "csr upload: rows [%lld, %lld) are not a range of the %lld rows",
+                (long long)row_begin, (long long)row_end, (long long)rows_total);
+  const int64_t p0 = row_ptr[row_begin], p1 = row_ptr[row_end];
+  if (p0 < 0 || p1 < p0)
+    return fail(ctx, SWB_ERR_INVALID_DATA, "row offsets must be non-decreasing, but rows %lld and %lld start at %lld and %lld",
+                (long long)row_begin, (long long)row_end, (long long)p0, (long long)p1);
+  std::vector<int32_t> rebased((size_t)(row_end - row_begin) + 1);
+  for (int64_t r = row_begin; r <= row_end; ++r) rebased[(size_t)(r - row_begin)] = (int32_t)(row_ptr[r] - p0);
+  return csr_upload_impl(ctx, row_end - row_begin, cols, p1 - p0, rebased.data(), col_idx ? col_idx + p0 : nullptr,
+                         val ? val + p0 : nullptr, true, out);
 }
 
 void swb_csr_release(swb_context *ctx, swb_csr_handle *h) {
@@ -1107,7 +1205,9 @@ int resident_host_call(swb_context *ctx, const swb_options *o, const swb_csr_han
 }  // extern "C++"
 
 int swb_spmv_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, const float *x, float *y) {
-  int st = check_ctx(ctx);
+  int st = reject_host_accumulate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
   if (!h || (h->cols > 0 && !x) || (h->rows > 0 && !y))
@@ -1122,7 +1222,9 @@ int swb_spmv_resident_host(swb_context *ctx, const swb_options *o, const swb_csr
 
 int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, int64_t n_rhs,
                            const float *B, float *C) {
-  int st = check_ctx(ctx);
+  int st = reject_host_accumulate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
   if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
@@ -1135,6 +1237,137 @@ int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr
                               return swb_spmm(ctx, opts, rows, h->cols, nnz, n_rhs, rp, ci, v, d_B, d_C,
                                               ctx->host_stream);
                             });
+}
+
+// ---- sharded operators: gather the dense operand, then the local kernel -----------------------
+
+extern "C++" {
+namespace {
+
+int grow(swb_context *ctx, char **buf, size_t *have, size_t need, const char *what) {
+  if (need <= *have) return SWB_OK;
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr;
+  *have = 0;
+  cudaError_t e = cudaMalloc(buf, need);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, what);
+  *have = need;
+  return SWB_OK;
+}
+
+// Every rank's chunk of the dense operand (cols x width floats, ceil(cols / ranks) rows per rank, this
+// rank's chunk at `owned`: device memory unless owned_on_host) gathered into one device copy, queued on
+// `s`.  The exchange is the peer-store kernel when the context has a window of that chunk size, else
+// ncclAllGather on the context's communicator; one rank needs neither.
+int gather_dense_operand(swb_context *ctx, const float *owned, bool owned_on_host, int64_t cols, int64_t width,
+                         cudaStream_t s, const float **full_out) {
+  const int ranks = ctx->comm ? ctx->comm_ranks : 1, rank = ctx->comm ? ctx->comm_rank : 0;
+  const int64_t chunk_rows = swb::ceil_div(cols, ranks);
+  int64_t own_begin = (int64_t)rank * chunk_rows, own_end = own_begin + chunk_rows;
+  if (own_begin > cols) own_begin = cols;
+  if (own_end > cols) own_end = cols;
+  const size_t own_bytes = (size_t)(own_end - own_begin) * width * 4, chunk_bytes = (size_t)chunk_rows * width * 4;
+  if (own_bytes > 0 && !owned) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "sharded operator: NULL dense operand");
+  const bool staged = owned_on_host || own_bytes != chunk_bytes || (reinterpret_cast<uintptr_t>(owned) & 15u) != 0;
+  const char *send = reinterpret_cast<const char *>(owned);
+  if (staged) {  // padded device copy of the chunk
+    int st = grow(ctx, &ctx->shard_send, &ctx->shard_send_bytes, chunk_bytes > 0 ? chunk_bytes : 16, "cudaMalloc(chunk)");
+    if (st != SWB_OK) return st;
+    if (own_bytes > 0)
+      SWB_CUDA(ctx, cudaMemcpyAsync(ctx->shard_send, owned, own_bytes,
+                                    owned_on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice, s));
+    if (chunk_bytes > own_bytes) SWB_CUDA(ctx, cudaMemsetAsync(ctx->shard_send + own_bytes, 0, chunk_bytes - own_bytes, s));
+    send = ctx->shard_send;
+  }
+  if (ranks == 1) {
+    *full_out = reinterpret_cast<const float *>(send);
+    return SWB_OK;
+  }
+  int64_t window_bytes = 0;
+  void *window = swb::peer_window_data(ctx, &window_bytes);
+  if (window && window_bytes == (int64_t)chunk_bytes && chunk_bytes % 16 == 0) {
+    int st = swb_comm_window_allgather(ctx, send, s);
+    if (st != SWB_OK) return st;
+    *full_out = static_cast<const float *>(window);
+    return SWB_OK;
+  }
+  int st = grow(ctx, &ctx->shard_full, &ctx->shard_full_bytes, chunk_bytes * (size_t)ranks, "cudaMalloc(gathered operand)");
+  if (st != SWB_OK) return st;
+  st = swb_comm_allgather(ctx, send, ctx->shard_full, (int64_t)chunk_bytes, s);
+  if (st != SWB_OK) return st;
+  *full_out = reinterpret_cast<const float *>(ctx->shard_full);
+  return SWB_OK;
+}
+
+}  // namespace
+}  // extern "C++"
+
+int swb_spmv_sharded(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz,
+                     const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *x_owned,
+                     float *y, swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (cols < 0) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: rows, cols and nnz must be non-negative");
+  const float *x = nullptr;
+  st = gather_dense_operand(ctx, x_owned, false, cols, 1, static_cast<cudaStream_t>(stream), &x);
+  if (st != SWB_OK) return st;
+  return swb_spmv(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
+}
+
+int swb_spmm_sharded(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz, int64_t n_rhs,
+                     const int32_t *row_ptr, const int32_t *col_idx, const float *val, const float *B_owned,
+                     float *C, swb_stream stream) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (cols < 0) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: rows, cols and nnz must be non-negative");
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  const float *B = nullptr;
+  st = gather_dense_operand(ctx, B_owned, false, cols, n_rhs, static_cast<cudaStream_t>(stream), &B);
+  if (st != SWB_OK) return st;
+  return swb_spmm(ctx, o, rows, cols, nnz, n_rhs, row_ptr, col_idx, val, B, C, stream);
+}
+
+// Host operands: this rank's chunk in, the exchange on the device, the local kernel, this rank's rows out.
+static int sharded_host_call(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, int64_t width,
+                             const float *owned_host, float *out_host, bool spmv) {
+  int st = reject_host_accumulate(ctx, o);
+  if (st != SWB_OK) return st;
+  st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
+  if (!h || (h->rows > 0 && !out_host))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "sharded operator: NULL matrix handle or operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  const size_t out_bytes = (size_t)h->rows * width * 4;
+  st = workspace_reserve(ctx, pad256(out_bytes));
+  if (st != SWB_OK) return st;
+  float *d_out = workspace_take<float>(ctx, h->rows * width);
+  cudaStream_t s = ctx->host_stream;
+  const float *dense = nullptr;
+  st = gather_dense_operand(ctx, owned_host, true, h->cols, width, s, &dense);
+  if (st == SWB_OK)
+    st = spmv ? swb_spmv(ctx, o, h->rows, h->cols, h->nnz, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense, d_out, s)
+              : swb_spmm(ctx, o, h->rows, h->cols, h->nnz, width, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense,
+                         d_out, s);
+  cudaError_t e = cudaSuccess;
+  if (st == SWB_OK && out_bytes > 0) e = cudaMemcpyAsync(out_host, d_out, out_bytes, cudaMemcpyDeviceToHost, s);
+  const cudaError_t e1 = cudaStreamSynchronize(s);  // also after an error: the copies touch caller memory
+  if (st != SWB_OK) return st;
+  if (e == cudaSuccess) e = e1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "sharded host call");
+  return SWB_OK;
+}
+
+int swb_spmv_sharded_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, const float *x_owned,
+                          float *y) {
+  return sharded_host_call(ctx, o, h, 1, x_owned, y, true);
+}
+
+int swb_spmm_sharded_host(swb_context *ctx, const swb_options *o, const swb_csr_handle *h, int64_t n_rhs,
+                          const float *B_owned, float *C) {
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  return sharded_host_call(ctx, o, h, n_rhs, B_owned, C, false);
 }
 
 // ---- memref-descriptor entry points -------------------------------------------------

@@ -14,6 +14,16 @@ namespace swb {
 SWB_HD int64_t ceil_div(int64_t a, int64_t b) { return a / b + (a % b != 0); }
 SWB_HD int64_t max1(int64_t v) { return v > 1 ? v : 1; }
 
+// Largest x dimension of a CUDA grid.  `blocks` (at least one block is always launched) as a grid
+// dimension, or false when it does not fit.
+constexpr int64_t kMaxGridX = 2147483647LL;
+inline bool grid_dim(int64_t blocks, unsigned *out) {
+  const int64_t b = max1(blocks);
+  if (b > kMaxGridX) return false;
+  *out = (unsigned)b;
+  return true;
+}
+
 // Balanced contiguous partition of [lower, upper) over `count` workers:
 // base = span / count, rem = span % count; worker w starts at
 // lower + w*base + min(w, rem) and takes base + (w < rem) positions

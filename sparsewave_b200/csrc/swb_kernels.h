@@ -54,6 +54,11 @@ struct DeviceInfo {
 cudaError_t launch_fill_zero(float *y, int64_t n, int block, cudaStream_t s,
                              int64_t *launches);
 
+// Roofline probe: streams col/val (nnz rounded down to a multiple of 4, both 16-byte aligned) and gathers
+// x[col[p]] with no row logic; products are added into the 1024 floats at `sink`.
+cudaError_t launch_stream_gather_probe(int64_t nnz, const int32_t *col, const float *val, const float *x, float *sink,
+                                       const DeviceInfo &dev, cudaStream_t s, int64_t *launches);
+
 // --- COO SpMV (zero fill + one atomic per nonzero)
 cudaError_t launch_coo_spmv_thread_per_nonzero(int64_t rows, int64_t nnz, const int32_t *row, const int32_t *col,
                                                const float *val, const float *x, float *y, int block,
@@ -72,12 +77,22 @@ cudaError_t launch_spmv_thread_per_position(const CsrSpmvArgs &a, int block,
                                             int64_t chunk, bool segmented,
                                             const PositionTrace &trace,
                                             cudaStream_t s, int64_t *launches);
-// `batch`: consecutive reference wave partitions walked by one warp (>= 1).
+// Long rows of a large matrix through shared-memory bands of x (spmv_band.cuh): `bands` bands of columns,
+// rows of at least `long_min` positions, room for `cap` such rows in the scratch memory.
+struct BandPlan {
+  int bands = 0, long_min = 0, cap = 0;
+};
+bool band_path_plan(const CsrSpmvArgs &a, int64_t min_nnz, BandPlan *plan);  // false: not taken (nnz < min_nnz, ...)
+size_t band_scratch_bytes(const BandPlan &plan);            // device scratch the path needs (256-byte aligned)
+// `batch`: consecutive reference wave partitions walked by one warp (>= 1).  `band` + `band_scratch`
+// (or NULL) switch the long-row path on; it replaces the zero-fill launch by three kernels.
 cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block,
                                           int64_t batch,
                                           const PositionTrace &trace,
                                           cudaStream_t s, int64_t *launches,
-                                          int64_t *physical_grid);
+                                          int64_t *physical_grid,
+                                          const BandPlan *band, void *band_scratch,
+                                          const DeviceInfo &dev);
 int64_t wave_per_position_auto_batch(int64_t nnz, int block,
                                      const DeviceInfo &dev);
 int64_t wave_per_position_physical_grid(int64_t nnz, int block, int64_t batch);
@@ -119,6 +134,8 @@ void set_context_comm(swb_context *ctx, void *comm, int n_ranks, int rank);
 bool context_comm_shape(const swb_context *ctx, int *n_ranks, int *rank);  // false without a communicator
 void *context_peer_window(const swb_context *ctx);
 void set_context_peer_window(swb_context *ctx, void *window);
+void *peer_window_data(const swb_context *ctx, int64_t *bytes_per_rank);  // NULL without a window
+void abandon_peer_window(swb_context *ctx);  // non-collective tear-down (swb_peer_window.cu)
 int *context_status_flag(const swb_context *ctx);
 void count_launch(swb_context *ctx);
 

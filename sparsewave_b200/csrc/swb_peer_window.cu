@@ -128,6 +128,27 @@ void release(PeerWindow *w) {
 }
 
 }  // namespace
+
+// This rank's window (past its header) and the bytes every rank contributes, or NULL without a window.
+void *peer_window_data(const swb_context *ctx, int64_t *bytes_per_rank) {
+  PeerWindow *w = static_cast<PeerWindow *>(context_peer_window(ctx));
+  if (!w) return nullptr;
+  *bytes_per_rank = w->bytes_per_rank;
+  return w->local + kHeaderBytes;
+}
+
+// Tear-down without a collective, for swb_destroy: the peers' windows are unmapped and the bookkeeping is
+// freed, but this rank's window stays allocated (a peer may still map it, and memory that another process
+// maps must not be freed), until the process ends.
+void abandon_peer_window(swb_context *ctx) {
+  PeerWindow *w = static_cast<PeerWindow *>(context_peer_window(ctx));
+  if (!w) return;
+  cudaSetDevice(context_device(ctx));
+  w->local = nullptr;  // left allocated on purpose
+  release(w);
+  set_context_peer_window(ctx, nullptr);
+}
+
 }  // namespace swb
 
 extern "C" {

@@ -73,3 +73,18 @@ def assert_within_bound(actual, expected, bound, rel=1e-5):
     bad = err > rel * np.asarray(bound) + 1e-30
     assert not bad.any(), (f"{int(bad.sum())} of {bad.size} outputs out of tolerance; worst "
                            f"err/bound = {np.max(err / (np.asarray(bound) + 1e-30)):.3e}")
+
+
+def assert_bf16_close(C, brp, bci, bv_bits, B_bits, bs):
+    """BF16 bar of the BSR path (1e-2 relative, read strictly): against the oracle's own rounded bits the output
+    may differ by one bf16 ulp (0.4 % to 0.8 %) wherever the exact sum is at least 2**-6 of the size of its terms;
+    outputs of cancelling sums are held to 1e-2 * 2**-6 of that size instead.  `C` is a bf16 CUDA or CPU tensor."""
+    import torch
+    import oracle
+    brp, bci = np.asarray(brp, np.int32), np.asarray(bci, np.int32)
+    bits, f32 = oracle.bsr_spmm_bf16(brp, bci, bv_bits, B_bits, bs)
+    bound = oracle.bsr_abs_bound_bf16(brp, bci, bv_bits, B_bits, bs)
+    got = C.detach().contiguous().view(torch.uint16).cpu().numpy()
+    off_by_more_than_an_ulp, cancelling_bad = oracle.bf16_mismatches(got, bits, f32, bound)
+    assert (off_by_more_than_an_ulp, cancelling_bad) == (0, 0)
+    return bits

@@ -243,4 +243,10 @@ def test_unaligned_operands_take_the_scalar_kernels(ctx):
     Bbo.copy_(Bb.reshape(-1))
     C1 = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, Bb, 16)
     C2 = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, Bbo.view(80, 16), 16)
-    assert float((C1.float() - C2.float()).abs().max()) <= 1e-2 * float(C1.float().abs().max() + 1)
+    # tensor-core and CUDA-core kernels add the same exact products in f32 in different orders: the rounded
+    # outputs differ by at most one bf16 ulp (two where both sit one ulp either side of the oracle's)
+    b1, b2 = C1.view(torch.int16).int(), C2.view(torch.int16).int()
+    o1, o2 = torch.where(b1 < 0, -(b1 & 0x7FFF), b1), torch.where(b2 < 0, -(b2 & 0x7FFF), b2)
+    big = C1.float().abs() >= 2.0 ** -4 * C1.float().abs().max()
+    assert int(((o1 - o2).abs() > 2)[big].sum()) == 0
+    assert float((C1.float() - C2.float()).abs().max()) <= 2.0 ** -7 * float(C1.float().abs().max())

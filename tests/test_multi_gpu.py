@@ -76,12 +76,31 @@ def _rank_main(rank, world, port):
         Cb = sharding.ShardedBsrOperator(ctx, bshard).spmm(Bb[blo:bhi].contiguous())
         whole = ctx.bsr_spmm("", bsr.block_row_ptr, bsr.block_col_idx, bsr.block_values, Bb, 16)
         assert torch.equal(Cb, whole[bshard.row_begin:bshard.row_end])
+        # the sharded step through host buffers: this rank's rows of the matrix uploaded once from the full host
+        # matrix, then only this rank's chunk of x (or B) goes in and only its rows come out
+        bnd = sharding.shard_boundaries(a.row_ptr, world)
+        resident = ctx.csr_upload_rows(a.cols, rp, ci, v, int(bnd[rank]), int(bnd[rank + 1]))
+        yh = np.empty(shard.rows, dtype=np.float32)
+        for scale in (1.0, 3.0):
+            resident.spmv_sharded_host("spmv-mapping=wave-per-position", np.ascontiguousarray(xh[lo:hi] * np.float32(scale)), yh)
+            want = oracle.csr_spmv(rp, ci, v, xh * np.float32(scale))[rows]
+            assert np.all(np.abs(yh - want) <= 1e-5 * scale * oracle.csr_abs_bound(rp, ci, v, xh)[rows] + 1e-30)
+        Ch = np.empty((shard.rows, 8), dtype=np.float32)
+        resident.spmm_sharded_host("spmm-mapping=wave-per-row-tile spmm-tile-size=8 spmm-block-size=128",
+                                   np.ascontiguousarray(Bh[lo:hi]), Ch)
+        assert np.all(np.abs(Ch - oracle.csr_spmm(rp, ci, v, Bh)[rows]) <= 1e-5 * bound + 1e-30)
+        with pytest.raises(Exception):  # the host calls' result buffer is write-only
+            resident.spmv_sharded_host("spmv-mapping=wave-per-position accumulate=1", np.ascontiguousarray(xh[lo:hi]), yh)
+        resident.release()
+        assert ctx.device_status() == 0
         # shard boundaries are the same on every rank
         b = torch.tensor(sharding.shard_boundaries(a.row_ptr, world), device="cuda")
         ref = b.clone()
         dist.broadcast(ref, 0)
         assert torch.equal(b, ref)
         dist.barrier()
+        ctx.window_destroy()  # collective tear-down, on the success path only
+        ctx.close()
     finally:
         dist.destroy_process_group()
 

@@ -5,7 +5,7 @@ import torch
 from hypothesis import HealthCheck, given, settings, strategies as st
 
 import oracle
-from tests.helpers import assert_within_bound, dev
+from tests.helpers import assert_bf16_close, assert_within_bound, dev
 
 pytestmark = pytest.mark.gpu
 
@@ -84,8 +84,5 @@ def test_bsr16_tensor_core_any_shape(ctx, brows, bcols, n8, density, seed):
     B = W.dense_normal((bcols * 16, n8 * 8), seed=seed)
     C = ctx.bsr_spmm("", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(), B.cuda(), 16)
     assert ctx.device_status() == 0
-    _, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.numpy(), a.block_col_idx.numpy(),
-                                  a.block_values.view(torch.uint16).numpy(), B.view(torch.uint16).numpy(), 16)
-    got = C.float().cpu().numpy()
-    scale = np.abs(f32) + 1e-2 * np.sqrt(np.diff(a.block_row_ptr.numpy()).repeat(16) * 16 + 1.0)[:, None]
-    assert np.all(np.abs(got - f32) <= 1e-2 * scale)
+    assert_bf16_close(C, a.block_row_ptr.numpy(), a.block_col_idx.numpy(), a.block_values.view(torch.uint16).numpy(),
+                      B.view(torch.uint16).numpy(), 16)

@@ -5,7 +5,8 @@ import torch
 
 import oracle
 from sparsewave_b200 import workloads as W
-from tests.helpers import (BSR_GOLDEN, SPMM_GOLDEN, SPMM_GOLDEN_TORCH, assert_within_bound, dev, random_csr)
+from tests.helpers import (BSR_GOLDEN, SPMM_GOLDEN, SPMM_GOLDEN_TORCH, assert_bf16_close, assert_within_bound, dev,
+                           random_csr)
 
 pytestmark = pytest.mark.gpu
 
@@ -136,13 +137,9 @@ def _bsr_bf16_case(ctx, grid_rows, grid_cols, bs, n, density, seed):
     B = W.dense_normal((grid_cols * bs, n), seed=seed)
     C = ctx.bsr_spmm("", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(), B.cuda(), bs)
     assert ctx.device_status() == 0  # no bounded wait of the tensor-core kernel gave up
-    bits, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.numpy(), a.block_col_idx.numpy(),
-                                     a.block_values.view(torch.uint16).numpy(), B.view(torch.uint16).numpy(), bs)
-    got = C.float().cpu().numpy()
-    # BF16 tolerance of the path: 1e-2 relative, measured against the size of the accumulated terms
-    scale = np.abs(f32) + 1e-2 * np.sqrt((np.diff(a.block_row_ptr.numpy()).repeat(bs) * bs)[:, None] + 1.0)
-    assert np.all(np.abs(got - f32) <= 1e-2 * scale), float(np.max(np.abs(got - f32) / scale))
-    return got, bits
+    bits = assert_bf16_close(C, a.block_row_ptr.numpy(), a.block_col_idx.numpy(),
+                             a.block_values.view(torch.uint16).numpy(), B.view(torch.uint16).numpy(), bs)
+    return C.float().cpu().numpy(), bits
 
 
 @pytest.mark.parametrize("bs", [4, 8, 16, 32])
@@ -160,12 +157,8 @@ def test_config_c5_reduced(ctx):
     a, B = W.config_c5(device="cuda", block_grid=256, n_rhs=512)
     C = ctx.bsr_spmm("", a.block_row_ptr, a.block_col_idx, a.block_values, B, 16)
     assert ctx.device_status() == 0
-    bits, f32 = oracle.bsr_spmm_bf16(a.block_row_ptr.cpu().numpy(), a.block_col_idx.cpu().numpy(),
-                                     a.block_values.view(torch.uint16).cpu().numpy(),
-                                     B.view(torch.uint16).cpu().numpy(), 16)
-    got = C.float().cpu().numpy()
-    scale = np.abs(f32) + 1e-2 * np.sqrt(np.diff(a.block_row_ptr.cpu().numpy()).repeat(16) * 16 + 1.0)[:, None]
-    assert np.all(np.abs(got - f32) <= 1e-2 * scale)
+    assert_bf16_close(C, a.block_row_ptr.cpu().numpy(), a.block_col_idx.cpu().numpy(),
+                      a.block_values.view(torch.uint16).cpu().numpy(), B.view(torch.uint16).cpu().numpy(), 16)
 
 
 def test_full_size_c4_properties(ctx):
@@ -212,8 +205,6 @@ def test_full_size_c5_properties(ctx):
     for b0 in (0, 500, 1024 - 8):
         sub = (brp[b0:b0 + 9] - brp[b0]).astype(np.int32)
         sl = slice(brp[b0], brp[b0 + 8])
-        _, f32 = oracle.bsr_spmm_bf16(sub, bci[sl], bv[sl.start * 256:sl.stop * 256], Bh, 16)
-        got = C[b0 * 16:(b0 + 8) * 16].float().cpu().numpy()
-        assert np.all(np.abs(got - f32) <= 1e-2 * (np.abs(f32) + 0.3))
+        assert_bf16_close(C[b0 * 16:(b0 + 8) * 16], sub, bci[sl], bv[sl.start * 256:sl.stop * 256], Bh, 16)
     # every output was written (no NaN from uninitialised memory) and the checksum matches the f64 total
     assert bool(torch.isfinite(C.float()).all())
