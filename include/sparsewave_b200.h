@@ -220,8 +220,8 @@ SWB_API int swb_bsr_spmm_bf16(swb_context *ctx, const swb_options *opts,
  * locked cannot do that.  This entry point takes no context, calls no
  * cudaMalloc / cudaFree and keeps its status words in a fixed 128 KiB array
  * inside the library image (held by every GPU that loads the library until
- * the process exits), one word per (block row, 128-column tile) pair.
- *   - Limit: (rows / 16) * ceil(n_rhs / 128) <= 32768, else SWB_ERR_CAPACITY.
+ * the process exits), one word per (block row, 256-column tile) pair.
+ *   - Limit: (rows / 16) * ceil(n_rhs / 256) <= 32768, else SWB_ERR_CAPACITY.
  *   - Needs nnzb > 0, n_rhs % 8 == 0 and 16-byte aligned block_values and B,
  *     else SWB_ERR_UNSUPPORTED (there is no second kernel behind it).
  *   - The first call on a device looks up the array's device address; make

@@ -7,30 +7,36 @@
 // with bf16 operands, f32 accumulation and one rounding to bf16 at the store.
 //
 // Mapping to the MMA.  A 16-row block would waste the M dimension (64 or 128)
-// of tcgen05.mma, so the product is formed transposed: for one block row and a
-// tile of 128 right-hand-side columns,
-//   D[m, r] (+)= sum_k  Bt[m, k] * At[k, r],   m = column in the tile, k = lc,
+// of tcgen05.mma, so the product is formed transposed: for one block row and
+// 128 right-hand-side columns,
+//   D[m, r] (+)= sum_k  Bt[m, k] * At[k, r],   m = column, k = lc,
 // one tcgen05.mma of shape M=128, N=16, K=16 per nonzero block, all blocks of
 // the block row accumulating into one 128-lane x 16-column f32 tile in TMEM.
-//   - MMA operand A = the 16 x 128 slab B[bci*16 .. +16, n0 .. n0+128).  Row k
-//     is contiguous along m: MN-major.  Two TMA boxes of 64 columns x 16 rows
-//     with the 128-byte swizzle land it as the canonical MN-major SWIZZLE_128B
-//     layout (128-byte rows, 1024 bytes between groups of 8 k rows = stride
-//     byte offset, 2048 bytes between the two 64-column halves = leading byte
-//     offset).  Columns past N are zero-filled by the TMA unit.
+// A CTA owns one block row and a tile of 256 right-hand-side columns, i.e. two
+// such accumulators side by side in TMEM (columns 0-15 and 16-31), so that each
+// block and each block-column index is fetched once per 256 columns.
+//   - MMA operand A = a 16 x 128 slab B[bci*16 .. +16, n .. n+128).  Row k is
+//     contiguous along m: MN-major.  Two TMA boxes of 64 columns x 16 rows with
+//     the 128-byte swizzle land it as the canonical MN-major SWIZZLE_128B layout
+//     (128-byte rows, 1024 bytes between groups of 8 k rows = stride byte
+//     offset, 2048 bytes between the two 64-column halves = leading byte
+//     offset).  Columns past N are zero-filled by the TMA unit; a tile whose
+//     second 128 columns lie wholly past N skips them.
 //   - MMA operand B = the block itself, [r][lc] row-major: K-major.  One TMA box
 //     of 16 x 16 with the 32-byte swizzle over the block values viewed as a
 //     (nnzb*16) x 16 matrix lands it as the canonical K-major SWIZZLE_32B layout
 //     (32-byte rows, 256 bytes between groups of 8 rows = stride byte offset).
-// The slab rows are gathered by block-column index, one box pair per block.
+//     Both accumulators' MMAs read the same copy.
+// The slab rows are gathered by block-column index, four boxes per block.
 //
-// Pipeline.  One thread is both producer and MMA issuer: it arms a stage's
-// `full` mbarrier with the byte count, issues the stage's TMA copies, and
-// STAGES-1 chunks later waits for that barrier and issues the chunk's MMAs;
-// tcgen05.commit arrives on the stage's `empty` mbarrier when the MMAs have
-// read their operands.  After the last chunk a commit arrives on `done`; the
-// four warps then read the accumulator with tcgen05.ld (each its own 32 TMEM
-// lanes), round to bf16 and store C.
+// Pipeline.  Lane 0 of warp 4 is the producer: per chunk of blocks it waits for
+// the stage's `empty` mbarrier, loads the chunk's block-column indices, arms the
+// stage's `full` mbarrier with the byte count and issues the TMA copies.  Lane 0
+// of warp 5 issues the MMAs: it waits for `full`, issues the chunk's MMAs and
+// lets tcgen05.commit arrive on `empty` when they have read their operands, so
+// index loads and copies of later chunks never wait behind a commit.  After the
+// last chunk the commit arrives on `done`; warps 0-3 then read both accumulators
+// with tcgen05.ld (each warp its own 32 TMEM lanes), round to bf16 and store C.
 //
 // Every mbarrier wait is bounded: when one runs out the kernel raises the
 // status word, frees its TMEM columns and returns.
@@ -46,25 +52,32 @@
 namespace swb {
 namespace {
 
-constexpr int TILE_N = 128;                  // right-hand-side columns per CTA (MMA M)
+constexpr int TILE_N = 256;                  // right-hand-side columns per CTA (two MMA M = 128 halves)
+constexpr int HALF_N = 128;
+// One block per stage, three stages (28 KiB of shared memory, seven CTAs per SM): on the 5 %-dense
+// 1024 x 1024 block grid with 512 columns, 69.7 us; (2,2) 75.7, (2,3) 80.0, (1,2) 78.7, (1,4) 84.0, (4,2) 86.0.
+// What counts is the number of CTAs in flight per SM, each being one serial chain of copies.
 #ifndef SWB_BSR_CHUNK
-#define SWB_BSR_CHUNK 2
+#define SWB_BSR_CHUNK 1
 #endif
 #ifndef SWB_BSR_STAGES
-#define SWB_BSR_STAGES 2
+#define SWB_BSR_STAGES 3
 #endif
 constexpr int CHUNK = SWB_BSR_CHUNK;         // blocks per pipeline stage
 constexpr int STAGES = SWB_BSR_STAGES;
-constexpr int SLAB_BYTES = 16 * TILE_N * 2;  // 4096: one 16 x 128 bf16 slab
-constexpr int HALF_SLAB = SLAB_BYTES / 2;    // 2048: 64 columns x 16 rows
+constexpr int BOX_BYTES = 16 * 64 * 2;       // 2048: 64 columns x 16 rows
+constexpr int HALF_SLAB = 2 * BOX_BYTES;     // 4096: one 16 x 128 bf16 slab (one accumulator's operand)
+constexpr int SLAB_BYTES = 2 * HALF_SLAB;    // 8192: 16 x 256
 constexpr int BLOCK_BYTES = 16 * 16 * 2;     // 512
 constexpr int STAGE_SLABS = CHUNK * SLAB_BYTES;
-constexpr int STAGE_BYTES = STAGE_SLABS + CHUNK * BLOCK_BYTES;  // slabs first (1024-aligned), then blocks
+// slabs first (1024-aligned), then blocks, padded so that the next stage's slabs are 1024-aligned again
+constexpr int STAGE_BYTES = (STAGE_SLABS + CHUNK * BLOCK_BYTES + 1023) / 1024 * 1024;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;         // + alignment slack
-constexpr int TMEM_COLS = 32;                // minimum allocation; 16 are used
+constexpr int TMEM_COLS = 32;                // two accumulators of 16 columns
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr int PRODUCER_THREAD = 128;         // lane 0 of a fifth warp issues TMA and MMA
-constexpr int THREADS = 160;
+constexpr int PRODUCER_THREAD = 128;         // lane 0 of warp 4 issues the TMA copies
+constexpr int MMA_THREAD = 160;              // lane 0 of warp 5 issues the MMAs
+constexpr int THREADS = 192;
 static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled slabs");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -109,7 +122,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 
 // PER_CTA_STATUS: raise status[blockIdx.x] instead of status[0] when a wait gives up.
 template <bool PER_CTA_STATUS>
-__global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
+__global__ void __launch_bounds__(THREADS) bsr16_spmm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_B, const __grid_constant__ CUtensorMap map_A, int64_t n_tiles,
     int64_t N, const int32_t *__restrict__ brp, const int32_t *__restrict__ bci, __nv_bfloat16 *__restrict__ C,
     int *status) {
@@ -123,13 +136,13 @@ __global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t br = blockIdx.x / n_tiles;
   const int n0 = (int)((blockIdx.x % n_tiles) * TILE_N);
+  const int halves = ((int64_t)n0 + HALF_N < N) ? 2 : 1;  // the second 128 columns may lie wholly past N
   const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int start = brp[br], end = brp[br + 1];
   const int nblk = end - start;
 
   if (nblk == 0) {  // empty block row: C = 0
-    const int64_t col = (int64_t)n0 + tid;
-    if (tid < TILE_N && col < N)
+    for (int64_t col = (int64_t)n0 + tid; col < N && col < (int64_t)n0 + TILE_N; col += THREADS)
       for (int r = 0; r < 16; ++r) C[(br * 16 + r) * N + col] = __float2bfloat16_rn(0.0f);
     return;
   }
@@ -155,60 +168,64 @@ __global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_slot;
+  const int nchunks = (nblk + CHUNK - 1) / CHUNK;
 
   if (tid == PRODUCER_THREAD) {
-    const int nchunks = (nblk + CHUNK - 1) / CHUNK;
-    bool ok = true;
-    // Iteration i produces chunk i (if any) and consumes chunk i - (STAGES-1).
-    for (int i = 0; i < nchunks + STAGES - 1 && ok; ++i) {
-      if (i < nchunks) {
-        const int s = i % STAGES;
-        if (i >= STAGES) {  // the MMAs of chunk i - STAGES must have read this stage
-          ok = mbar_wait(smem_u32(&bar_empty[s]), ((i / STAGES) - 1) & 1u);
-          if (!ok) break;
-        }
-        const int first = start + i * CHUNK;
-        const int count = min(CHUNK, end - first);
-        int bcs[CHUNK];
-#pragma unroll
-        for (int j = 0; j < CHUNK; ++j) bcs[j] = (j < count) ? __ldg(bci + first + j) : 0;
-        const uint32_t full = smem_u32(&bar_full[s]);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full),
-                     "r"((uint32_t)count * (SLAB_BYTES + BLOCK_BYTES))
-                     : "memory");
-        const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
-#pragma unroll
-        for (int j = 0; j < CHUNK; ++j) {
-          if (j >= count) break;
-          const uint32_t slab = sbase + (uint32_t)j * SLAB_BYTES;
-          tma_load_2d(slab, &map_B, n0, bcs[j] * 16, full);
-          tma_load_2d(slab + HALF_SLAB, &map_B, n0 + 64, bcs[j] * 16, full);
-          tma_load_2d(sbase + STAGE_SLABS + (uint32_t)j * BLOCK_BYTES, &map_A, 0, (first + j) * 16, full);
-        }
+    for (int i = 0; i < nchunks; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES && !mbar_wait(smem_u32(&bar_empty[s]), ((i / STAGES) - 1) & 1u)) {
+        failed = 1;  // the MMAs of chunk i - STAGES never released this stage
+        atomicExch(status + (PER_CTA_STATUS ? blockIdx.x : 0), 1);
+        break;
       }
-      const int c = i - (STAGES - 1);
-      if (c >= 0) {
-        const int s = c % STAGES;
-        ok = mbar_wait(smem_u32(&bar_full[s]), (c / STAGES) & 1u);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
-        const int count = min(CHUNK, nblk - c * CHUNK);
-        for (int j = 0; j < count; ++j) {
-          const uint64_t adesc = make_desc(sbase + (uint32_t)j * SLAB_BYTES, 2048u, 1024u, 2u);
-          const uint64_t bdesc = make_desc(sbase + STAGE_SLABS + (uint32_t)j * BLOCK_BYTES, 16u, 256u, 6u);
-          const uint32_t accumulate = (c > 0 || j > 0) ? 1u : 0u;
+      const int first = start + i * CHUNK;
+      const int count = min(CHUNK, end - first);
+      int bcs[CHUNK];
+#pragma unroll
+      for (int j = 0; j < CHUNK; ++j) bcs[j] = (j < count) ? __ldg(bci + first + j) : 0;
+      const uint32_t full = smem_u32(&bar_full[s]);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full),
+                   "r"((uint32_t)count * (uint32_t)(halves * HALF_SLAB + BLOCK_BYTES))
+                   : "memory");
+      const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+      for (int j = 0; j < CHUNK; ++j) {
+        if (j >= count) break;
+        const uint32_t slab = sbase + (uint32_t)j * SLAB_BYTES;
+        tma_load_2d(slab, &map_B, n0, bcs[j] * 16, full);
+        tma_load_2d(slab + BOX_BYTES, &map_B, n0 + 64, bcs[j] * 16, full);
+        if (halves == 2) {
+          tma_load_2d(slab + 2 * BOX_BYTES, &map_B, n0 + 128, bcs[j] * 16, full);
+          tma_load_2d(slab + 3 * BOX_BYTES, &map_B, n0 + 192, bcs[j] * 16, full);
+        }
+        tma_load_2d(sbase + STAGE_SLABS + (uint32_t)j * BLOCK_BYTES, &map_A, 0, (first + j) * 16, full);
+      }
+    }
+  } else if (tid == MMA_THREAD) {
+    bool ok = true;
+    for (int c = 0; c < nchunks; ++c) {
+      const int s = c % STAGES;
+      ok = mbar_wait(smem_u32(&bar_full[s]), (c / STAGES) & 1u);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sbase = stage0 + (uint32_t)s * STAGE_BYTES;
+      const int count = min(CHUNK, nblk - c * CHUNK);
+      for (int j = 0; j < count; ++j) {
+        const uint64_t bdesc = make_desc(sbase + STAGE_SLABS + (uint32_t)j * BLOCK_BYTES, 16u, 256u, 6u);
+        const uint32_t accumulate = (c > 0 || j > 0) ? 1u : 0u;
+        for (int h = 0; h < halves; ++h) {
+          const uint64_t adesc = make_desc(sbase + (uint32_t)j * SLAB_BYTES + (uint32_t)h * HALF_SLAB, 2048u, 1024u, 2u);
           asm volatile(
               "{\n\t.reg .pred p;\n\t"
               "setp.ne.b32 p, %4, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem),
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem + (uint32_t)h * 16u),
               "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
               : "memory");
         }
-        const uint32_t arrive_on = (c == nchunks - 1) ? smem_u32(&bar_done) : smem_u32(&bar_empty[s]);
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(arrive_on)
-                     : "memory");
       }
+      const uint32_t arrive_on = (c == nchunks - 1) ? smem_u32(&bar_done) : smem_u32(&bar_empty[s]);
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(arrive_on)
+                   : "memory");
     }
     if (!ok) {
       failed = 1;
@@ -224,20 +241,23 @@ __global__ void __launch_bounds__(160) bsr16_spmm_tcgen05_kernel(
   if (!done_ok && tid == 0) atomicExch(status + (PER_CTA_STATUS ? blockIdx.x : 0), 1);
 
   if (done_ok && !failed && warp < 4) {
-    uint32_t v[16];
-    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
-        "%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    const int64_t col = (int64_t)n0 + warp * 32 + lane;  // TMEM lane m = column n0 + m of C
-    if (col < N) {
+    // TMEM lane m of accumulator h = column n0 + 128 h + m of C; this warp reads lanes 32 warp .. +32
+    for (int h = 0; h < halves; ++h) {
+      uint32_t v[16];
+      const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)h * 16u;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+          "%15}, [%16];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const int64_t col = (int64_t)n0 + h * HALF_N + warp * 32 + lane;
+      if (col < N) {
 #pragma unroll
-      for (int r = 0; r < 16; ++r) C[(br * 16 + r) * N + col] = __float2bfloat16_rn(__uint_as_float(v[r]));
+        for (int r = 0; r < 16; ++r) C[(br * 16 + r) * N + col] = __float2bfloat16_rn(__uint_as_float(v[r]));
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -334,7 +354,7 @@ cudaError_t launch_bsr16_spmm_tcgen05(const BsrSpmmArgs &a, int *status_flag, co
 // which is part of the library image: every GPU that loads the library holds
 // its 128 KiB until the process exits, whether or not this entry point is used.
 //
-// One status word per CTA (block row x tile of 128 columns), hence the limit
+// One status word per CTA (block row x tile of 256 columns), hence the limit
 // of SWB_STATIC_MAX_CTAS CTAs per call.  All calls share the array and a call
 // begins by clearing the words it will use, so the array holds the outcome of
 // the most recent call only, and two calls that overlap on the GPU (different
@@ -432,7 +452,7 @@ extern "C" __attribute__((visibility("default"))) int swb_bsr16_spmm_bf16_static
   const int64_t grid = (rows / 16) * n_tiles;
   if (grid > SWB_STATIC_MAX_CTAS)
     return static_fail(kCapacity,
-                       "the static-scratch BSR entry point handles at most %lld (block row, 128-column tile) pairs "
+                       "the static-scratch BSR entry point handles at most %lld (block row, 256-column tile) pairs "
                        "per call, but this call needs %lld",
                        (long long)SWB_STATIC_MAX_CTAS, (long long)grid);
   if (grid == 0) return 0;

@@ -812,8 +812,12 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   // 16-byte aligned col/val); batch == 1 is the reference schedule, one
   // partition per warp and lane == position.  Blocks above 512 threads need
   // the register-capped instantiation.
-  const bool span = batch >= 2 && aligned16(a.col_idx) && aligned16(a.val);
-  const bool banded = span && band && band_scratch && !trace.enabled();
+  // col and val views that start the same number of elements past a 16-byte boundary take the span kernel
+  // too (it reads from that boundary); other misalignments take the scalar kernel.
+  const uintptr_t col_off = reinterpret_cast<uintptr_t>(a.col_idx) & 15u, val_off = reinterpret_cast<uintptr_t>(a.val) & 15u;
+  const bool span = batch >= 2 && col_off == val_off && col_off % 4 == 0 && a.nnz > 0;
+  const int shift = span ? (int)(col_off / 4) : 0;
+  const bool banded = span && shift == 0 && band && band_scratch && !trace.enabled();
   int long_min = 0;
   int *count = nullptr, *long_rows = nullptr, *tab = nullptr;
   if (banded) {
@@ -853,7 +857,7 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   do {                                                                                    \
     if (span)                                                                             \
       spmv_wave_span_kernel<TR, MB><<<(unsigned)grid, block, span_smem, s>>>(              \
-          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace, long_min); \
+          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace, long_min, shift); \
     else                                                                                  \
       spmv_wave_per_position_kernel<TR, MB><<<(unsigned)grid, block, smem, s>>>(           \
           a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);      \

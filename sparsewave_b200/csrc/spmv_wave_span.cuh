@@ -28,6 +28,11 @@
 // of the lane below.  One atomicAdd per (row, span) segment; the segment still
 // open at the end of a chunk is carried in registers.
 //
+// shift (0..3): col and val are views that start `shift` elements past a 16-byte boundary (the same for
+// both).  The kernel then reads from the boundary before them and works in positions p + shift, which keeps
+// every 128-bit load aligned; the up to three elements in front of the arrays share their 16-byte granule
+// with the first element and are masked like any position outside the span.
+//
 // long_min > 0: rows of at least long_min (>= 256) positions belong to the band kernel
 // (spmv_band.cuh) and are left out here.  A row that long is never inside one chunk, so only the row that
 // enters a chunk and the row that leaves it can be long: chunks that lie wholly in such a row are jumped
@@ -55,7 +60,7 @@ template <bool TRACE, int MAX_BLOCK>
 __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
     int64_t rows, int64_t nnz, int64_t wave_count, int64_t batch, const int32_t *__restrict__ row_ptr,
     const int32_t *__restrict__ col, const float *__restrict__ val, const float *__restrict__ x,
-    float *__restrict__ y, PositionTrace trace, int long_min) {
+    float *__restrict__ y, PositionTrace trace, int long_min, int shift) {
   extern __shared__ int smem_rows[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -68,11 +73,20 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
   const int64_t w1 = (w0 + batch < wave_count) ? w0 + batch : wave_count;
   const int64_t base = nnz / wave_count, rem = nnz % wave_count;
   auto wave_begin = [&](int64_t w) { return w * base + (w < rem ? w : rem); };
-  const int sb = (int)wave_begin(w0), se = (int)wave_begin(w1);
+  // from here on positions are shifted: p + shift, array element p + shift of the aligned views below
+  const int sb = (int)wave_begin(w0) + shift, se = (int)wave_begin(w1) + shift;
   if (sb >= se) return;
-  // Reference wave that owns a position (inverse of wave_begin), for the trace.
-  auto wave_of = [&](int p) -> int {
-    const int64_t split = rem * (base + 1);
+  nnz += shift;
+  col -= shift;
+  val -= shift;
+  if (TRACE) {
+    trace.row_of_position -= shift;
+    trace.worker_of_position -= shift;
+    trace.segment_end -= shift;
+  }
+  // Reference wave that owns a (shifted) position (inverse of wave_begin), for the trace.
+  auto wave_of = [&](int ps) -> int {
+    const int64_t p = ps - shift, split = rem * (base + 1);
     return (int)(p < split ? p / (base + 1) : rem + (p - split) / base);
   };
 
@@ -80,10 +94,10 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
   const int4 *col4 = reinterpret_cast<const int4 *>(col);
   const float4 *val4 = reinterpret_cast<const float4 *>(val);
 
-  int R = warp_row_search(row_ptr, (int)rows + 1, sb, lane);
-  int next_b = __ldg(row_ptr + R + 1);  // first position of the next non-empty row (or nnz)
+  int R = warp_row_search(row_ptr, (int)rows + 1, sb - shift, lane);
+  int next_b = __ldg(row_ptr + R + 1) + shift;  // first position of the next non-empty row (or nnz)
   // the row that enters the current chunk belongs to the band kernel
-  bool head_long = long_min > 0 && next_b - __ldg(row_ptr + R) >= long_min;
+  bool head_long = long_min > 0 && next_b - shift - __ldg(row_ptr + R) >= long_min;
   if (head_long && next_b >= se) return;  // the whole span lies inside a long row
   int carry_row = -1;
   float acc = 0.0f;
@@ -160,7 +174,7 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
     for (int64_t r0 = (int64_t)R + 1;; r0 += 32) {
       const int64_t r = r0 + lane;
       int b = 0x7fffffff;
-      if (r <= rows) b = __ldg(row_ptr + r);
+      if (r <= rows) b = __ldg(row_ptr + r) + shift;
       const bool inside = b < ce;
       if (inside) atomicMax(&marks[b - cb], (int)r);
       if (__ballot_sync(FULL, inside) != FULL) break;
@@ -260,7 +274,7 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
     acc = (lane == 31) ? S : 0.0f;
     carry_last = ce - 1;
     R = R_last;
-    next_b = __ldg(row_ptr + R + 1);
+    next_b = __ldg(row_ptr + R + 1) + shift;
     head_long = tail_long;
   }
   if (carry_row >= 0) {

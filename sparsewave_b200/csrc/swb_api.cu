@@ -697,7 +697,15 @@ int swb_spmm(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
   cudaError_t e = cudaSuccess;
   switch (o->spmm_mapping) {
     case SWB_THREAD_PER_OUTPUT: e = swb::launch_spmm_thread_per_output(a, Bs, s, &ctx->launches); break;
-    case SWB_WAVE_PER_ROW_TILE: e = swb::launch_spmm_wave_per_row_tile(a, Bs, (int)o->spmm_tile_size, s, &ctx->launches); break;
+    case SWB_WAVE_PER_ROW_TILE:
+      // Opt-in (SWB_SPMM_STAGED=1): the rows of B around the diagonal staged in shared memory by TMA, for
+      // banded matrices.  Measured on a banded-plus-random matrix it does not beat the fused-row kernel (the
+      // random half of the nonzeros keeps the step DRAM-bound), so it is not the default.
+      if (env_i64_or_zero("SWB_SPMM_STAGED", 0) > 0 && swb::spmm_staged_supported(a))
+        e = swb::launch_spmm_row_block_staged(a, ctx->status_flag, s, &ctx->launches);
+      else
+        e = swb::launch_spmm_wave_per_row_tile(a, Bs, (int)o->spmm_tile_size, s, &ctx->launches);
+      break;
     case SWB_SPMM_THREAD_PER_POSITION:
       e = swb::launch_spmm_thread_per_position(a, Bs, o->spmm_position_chunk_size, s, &ctx->launches);
       break;
@@ -1259,8 +1267,12 @@ int grow(swb_context *ctx, char **buf, size_t *have, size_t need, const char *wh
 // rank's chunk at `owned`: device memory unless owned_on_host) gathered into one device copy, queued on
 // `s`.  The exchange is the peer-store kernel when the context has a window of that chunk size, else
 // ncclAllGather on the context's communicator; one rank needs neither.
+// `zero` (or NULL): an output vector the consumer wants zero-filled first; the peer-store kernel does it
+// on the side and *zero_filled says so.
 int gather_dense_operand(swb_context *ctx, const float *owned, bool owned_on_host, int64_t cols, int64_t width,
-                         cudaStream_t s, const float **full_out) {
+                         cudaStream_t s, const float **full_out, float *zero = nullptr, int64_t zero_count = 0,
+                         bool *zero_filled = nullptr) {
+  if (zero_filled) *zero_filled = false;
   const int ranks = ctx->comm ? ctx->comm_ranks : 1, rank = ctx->comm ? ctx->comm_rank : 0;
   const int64_t chunk_rows = swb::ceil_div(cols, ranks);
   int64_t own_begin = (int64_t)rank * chunk_rows, own_end = own_begin + chunk_rows;
@@ -1286,8 +1298,9 @@ int gather_dense_operand(swb_context *ctx, const float *owned, bool owned_on_hos
   int64_t window_bytes = 0;
   void *window = swb::peer_window_data(ctx, &window_bytes);
   if (window && window_bytes == (int64_t)chunk_bytes && chunk_bytes % 16 == 0) {
-    int st = swb_comm_window_allgather(ctx, send, s);
+    int st = swb::window_allgather_and_fill(ctx, send, zero, zero_count, s);
     if (st != SWB_OK) return st;
+    if (zero && zero_filled) *zero_filled = true;
     *full_out = static_cast<const float *>(window);
     return SWB_OK;
   }
@@ -1308,10 +1321,18 @@ int swb_spmv_sharded(swb_context *ctx, const swb_options *o, int64_t rows, int64
   int st = check_ctx(ctx);
   if (st != SWB_OK) return st;
   if (cols < 0) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmv: rows, cols and nnz must be non-negative");
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
   const float *x = nullptr;
-  st = gather_dense_operand(ctx, x_owned, false, cols, 1, static_cast<cudaStream_t>(stream), &x);
+  // a position mapping starts from a zero-filled y: the exchange kernel fills it while it waits for the peers
+  const bool wants_fill = is_position_mapping(o->mapping) && !o->accumulate && rows > 0 && y;
+  bool filled = false;
+  st = gather_dense_operand(ctx, x_owned, false, cols, 1, static_cast<cudaStream_t>(stream), &x,
+                            wants_fill ? y : nullptr, rows, &filled);
   if (st != SWB_OK) return st;
-  return swb_spmv(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
+  if (!filled) return swb_spmv(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
+  swb_options add = *o;
+  add.accumulate = 1;
+  return swb_spmv(ctx, &add, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
 }
 
 int swb_spmm_sharded(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz, int64_t n_rhs,
@@ -1345,10 +1366,14 @@ static int sharded_host_call(swb_context *ctx, const swb_options *o, const swb_c
   float *d_out = workspace_take<float>(ctx, h->rows * width);
   cudaStream_t s = ctx->host_stream;
   const float *dense = nullptr;
-  st = gather_dense_operand(ctx, owned_host, true, h->cols, width, s, &dense);
+  const bool wants_fill = spmv && is_position_mapping(o->mapping) && h->rows > 0;
+  bool filled = false;
+  st = gather_dense_operand(ctx, owned_host, true, h->cols, width, s, &dense, wants_fill ? d_out : nullptr, h->rows, &filled);
+  swb_options local = *o;
+  if (filled) local.accumulate = 1;
   if (st == SWB_OK)
-    st = spmv ? swb_spmv(ctx, o, h->rows, h->cols, h->nnz, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense, d_out, s)
-              : swb_spmm(ctx, o, h->rows, h->cols, h->nnz, width, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense,
+    st = spmv ? swb_spmv(ctx, &local, h->rows, h->cols, h->nnz, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense, d_out, s)
+              : swb_spmm(ctx, &local, h->rows, h->cols, h->nnz, width, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense,
                          d_out, s);
   cudaError_t e = cudaSuccess;
   if (st == SWB_OK && out_bytes > 0) e = cudaMemcpyAsync(out_host, d_out, out_bytes, cudaMemcpyDeviceToHost, s);

@@ -105,6 +105,11 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block,
                                           int64_t *launches);
 // CUDA blocks launch_spmm_wave_per_row_tile uses when B and C are 16-byte aligned.
 int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs, int block, int tile);
+// wave-per-row-tile with a TMA-staged window of B rows around the diagonal in shared memory (spmm_staged.cu):
+// 1024 matrix rows x 16 right-hand-side columns per CTA.  `status_flag`: device int raised when the bounded
+// TMA wait gives up.
+bool spmm_staged_supported(const CsrSpmmArgs &a);
+cudaError_t launch_spmm_row_block_staged(const CsrSpmmArgs &a, int *status_flag, cudaStream_t s, int64_t *launches);
 cudaError_t launch_spmm_thread_per_position(const CsrSpmmArgs &a, int block,
                                             int64_t chunk, cudaStream_t s,
                                             int64_t *launches);
@@ -135,6 +140,8 @@ bool context_comm_shape(const swb_context *ctx, int *n_ranks, int *rank);  // fa
 void *context_peer_window(const swb_context *ctx);
 void set_context_peer_window(swb_context *ctx, void *window);
 void *peer_window_data(const swb_context *ctx, int64_t *bytes_per_rank);  // NULL without a window
+// swb_comm_window_allgather whose kernel also zero-fills zero[0 .. zero_count) (NULL: no fill)
+int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, int64_t zero_count, cudaStream_t stream);
 void abandon_peer_window(swb_context *ctx);  // non-collective tear-down (swb_peer_window.cu)
 int *context_status_flag(const swb_context *ctx);
 void count_launch(swb_context *ctx);

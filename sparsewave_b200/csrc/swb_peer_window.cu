@@ -6,13 +6,18 @@
 //   1. tells every peer "I no longer read my window" (ready flag, epoch-numbered; stream order guarantees
 //      that the kernel that consumed the previous epoch has finished),
 //   2. waits until every peer has said the same, so no window is overwritten while it is read,
-//   3. stores its own chunk into every rank's window (plain 16-byte peer stores; its own window included),
-//   4. once all its CTAs have fenced their stores, raises its done flag in every window,
-//   5. waits until every peer's done flag is up, so that the kernel after it finds the window complete.
-// All waits poll flags in this GPU's own memory that only the other ranks write, are bounded, and give up
+//   3. stores its own chunk into every rank's window (plain 16-byte peer stores; its own window included);
+//      each CTA serves one destination,
+//   4. per CTA: once its stores are ordered system-wide (one fence by one thread behind a CTA barrier), adds
+//      one to the destination's arrival counter with a remote atomic,
+//   5. the CTA of this rank that finishes last waits until this rank's own counter shows the arrivals of
+//      every rank's CTAs for this epoch, so that the kernel after it finds the window complete.
+// Optionally the kernel also zero-fills an output vector (the separate fill launch of the position
+// mappings) while it would otherwise wait.
+// All waits poll counters in this GPU's own memory that the other ranks write, are bounded, and give up
 // by setting the context's status word (swb_device_status) instead of spinning on; CTAs of one grid never
 // wait for one another, so the grid needs no co-residency.
-// Plain loads and stores only.  Not a reference feature.
+// Plain loads, stores and atomics only.  Not a reference feature.
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -28,22 +33,23 @@ namespace {
 
 constexpr int kMaxRanks = 16;
 constexpr int64_t kHeaderBytes = 4096;
-constexpr int kReadyOff = 0, kDoneOff = 256, kEpochOff = 512, kArrivedOff = 516;
-constexpr unsigned kPollLimit = 1u << 24;  // polls of a flag in local memory, 100 ns apart (a few seconds), before giving up
+// header words: ready[rank] at 0, arrivals (of all ranks' CTAs, ever) at 256, epoch at 512, local CTA count at 516
+constexpr int kReadyOff = 0, kArrivalsOff = 256, kEpochOff = 512, kCountOff = 516;
+constexpr unsigned kPollLimit = 1u << 24;  // polls of a word in local memory, 100 ns apart (a few seconds), before giving up
 constexpr int kGridTarget = 256;           // CTAs of a step, split evenly over the destination ranks
 
 struct PeerWindow {
-  int ranks = 1, rank = 0;
+  int ranks = 1, rank = 0, slices = 1;
   int64_t bytes_per_rank = 0;
   char *local = nullptr;
   char *peer[kMaxRanks] = {};
   char **d_peer = nullptr;
 };
 
-// true when flag[i] has reached `epoch` (epochs compared modulo 2^32) before the poll limit
-__device__ bool wait_flag(const volatile unsigned *flag, unsigned epoch) {
+// true when *word has reached `target` (compared modulo 2^32) before the poll limit
+__device__ bool wait_word(const volatile unsigned *word, unsigned target) {
   for (unsigned n = 0; n < kPollLimit; ++n) {
-    if ((int)(*flag - epoch) >= 0) return true;
+    if ((int)(*word - target) >= 0) return true;
     __nanosleep(100);
   }
   return false;
@@ -51,7 +57,8 @@ __device__ bool wait_flag(const volatile unsigned *flag, unsigned epoch) {
 
 __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restrict__ send, int64_t n16,
                                                              char *const *__restrict__ peer, int rank, int ranks,
-                                                             int64_t bytes_per_rank, int *status) {
+                                                             int64_t bytes_per_rank, float *__restrict__ zero,
+                                                             int64_t zero_count, int *status) {
   char *local = peer[rank];
   __shared__ unsigned s_epoch;
   __shared__ int s_failed;
@@ -64,11 +71,15 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restr
   __syncthreads();
   const unsigned epoch = s_epoch;
 
-  // 1. ready flags out (one CTA is enough), 2. ready flags in (every CTA looks for itself)
+  // 1. ready flags out (one CTA is enough)
   if (blockIdx.x == 0 && threadIdx.x < ranks)
     reinterpret_cast<volatile unsigned *>(peer[threadIdx.x] + kReadyOff)[rank] = epoch;
+  // the zero fill of the consumer's output rides along while the flags travel
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < zero_count; i += (int64_t)gridDim.x * blockDim.x)
+    zero[i] = 0.0f;
+  // 2. ready flags in (every CTA looks for itself)
   if (threadIdx.x < ranks && threadIdx.x != rank &&
-      !wait_flag(reinterpret_cast<volatile unsigned *>(local + kReadyOff) + threadIdx.x, epoch))
+      !wait_word(reinterpret_cast<volatile unsigned *>(local + kReadyOff) + threadIdx.x, epoch))
     s_failed = 1;
   __syncthreads();
 
@@ -86,27 +97,24 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restr
   }
   for (; i < n16; i += stride) out[i] = __ldg(send + i);
 
-  // 4. the CTA's stores are ordered before its count; the CTA that counts last speaks for the rank
-  __threadfence_system();
+  // 4. the CTA's stores (ordered before thread 0 by the barrier, system-wide by its fence) precede its
+  //    arrival at the destination; the CTA of this rank that counts last waits for the arrivals here
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned before = atomicAdd(reinterpret_cast<unsigned *>(local + kArrivedOff), 1u);
+    __threadfence_system();
+    atomicAdd_system(reinterpret_cast<unsigned *>(peer[dst] + kArrivalsOff), 1u);
+    const unsigned before = atomicAdd(reinterpret_cast<unsigned *>(local + kCountOff), 1u);
     s_last = before == gridDim.x - 1;
+    if (s_failed) atomicExch(status, 3);
   }
   __syncthreads();
-  if (s_failed && threadIdx.x == 0) atomicExch(status, 3);
   if (!s_last) return;
 
-  __threadfence_system();
-  if (threadIdx.x < ranks) reinterpret_cast<volatile unsigned *>(peer[threadIdx.x] + kDoneOff)[rank] = epoch;
-  // 5. every peer's chunk has landed here
-  if (threadIdx.x < ranks && threadIdx.x != rank &&
-      !wait_flag(reinterpret_cast<volatile unsigned *>(local + kDoneOff) + threadIdx.x, epoch))
-    atomicExch(status, 4);
-  __threadfence_system();
-  __syncthreads();
+  // 5. every rank's CTAs aimed at this rank (slices per rank, so gridDim.x per epoch) have arrived
   if (threadIdx.x == 0) {
-    *reinterpret_cast<volatile unsigned *>(local + kArrivedOff) = 0u;
+    if (!wait_word(reinterpret_cast<volatile unsigned *>(local + kArrivalsOff), epoch * gridDim.x)) atomicExch(status, 4);
+    __threadfence_system();
+    *reinterpret_cast<volatile unsigned *>(local + kCountOff) = 0u;
     *reinterpret_cast<volatile unsigned *>(local + kEpochOff) = epoch;
   }
 }
@@ -176,6 +184,7 @@ int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **wind
   // rank is left waiting in a collective and no rank ends up with a window that a peer lacks.
   PeerWindow *w = new PeerWindow();
   w->ranks = ranks; w->rank = rank; w->bytes_per_rank = bytes_per_rank;
+  w->slices = kGridTarget / ranks > 0 ? kGridTarget / ranks : 1;
   const size_t total = (size_t)kHeaderBytes + (size_t)ranks * (size_t)bytes_per_rank;
   struct Slot { cudaIpcMemHandle_t handle; int ok; int pad[3]; };  // one exchanged record, 80 bytes
   Slot *d_slots = nullptr;  // [0, ranks): gathered, [ranks]: this rank's
@@ -249,7 +258,16 @@ int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **wind
 }
 
 int swb_comm_window_allgather(swb_context *ctx, const void *send, swb_stream stream) {
-  using namespace swb;
+  return swb::window_allgather_and_fill(ctx, send, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+namespace swb {
+
+// The exchange of swb_comm_window_allgather; the same kernel also stores `zero_count` zeros at `zero`
+// (the output vector of the operator that consumes the window), or nothing when zero is NULL.
+int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, int64_t zero_count, cudaStream_t stream) {
   if (!ctx) {
     set_thread_error("context is NULL");
     return SWB_ERR_INVALID_ARGUMENT;
@@ -260,16 +278,20 @@ int swb_comm_window_allgather(swb_context *ctx, const void *send, swb_stream str
     return window_fail(ctx, SWB_ERR_INVALID_ARGUMENT, "window all-gather", "send must be a 16-byte aligned device pointer");
   cudaError_t e = cudaSetDevice(context_device(ctx));
   if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "cudaSetDevice", cudaGetErrorString(e));
-  // enough 16-byte loads in flight (16 KiB per CTA) to keep the NVLink egress busy whatever the rank count
-  const int slices = kGridTarget / w->ranks > 0 ? kGridTarget / w->ranks : 1;
-  peer_allgather_kernel<<<(unsigned)(w->ranks * slices), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  // enough 16-byte loads in flight (16 KiB per CTA) to keep the NVLink egress busy whatever the rank count;
+  // the grid is the same on every rank and for every step of a window (the arrival count relies on it)
+  peer_allgather_kernel<<<(unsigned)(w->ranks * w->slices), 256, 0, stream>>>(
       static_cast<const int4 *>(send), w->bytes_per_rank / 16, w->d_peer, w->rank, w->ranks, w->bytes_per_rank,
-      context_status_flag(ctx));
+      zero, zero ? zero_count : 0, context_status_flag(ctx));
   count_launch(ctx);
   e = cudaGetLastError();
   if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "window all-gather launch", cudaGetErrorString(e));
   return SWB_OK;
 }
+
+}  // namespace swb
+
+extern "C" {
 
 void swb_comm_window_destroy(swb_context *ctx) {
   using namespace swb;

@@ -2,6 +2,7 @@
 declared symbol, option parsing / validation reproduce the reference's
 diagnostics, index helpers match the oracle and the reference's folded
 answers, launch geometry follows the reference's grid arithmetic."""
+import ctypes as C
 import re
 from pathlib import Path
 
@@ -222,3 +223,39 @@ def test_headers_are_plain_c(tmp_path):
     inc = str(ROOT / "include")
     subprocess.run([gcc, "-std=c99", "-pedantic", "-Werror", "-Wall", "-I", inc, "-fsyntax-only", str(src)], check=True)
     subprocess.run([gxx, "-std=c++17", "-Werror", "-Wall", "-I", inc, "-fsyntax-only", "-x", "c++", str(src)], check=True)
+
+
+def test_launches_beyond_the_cuda_grid_limit_are_refused():
+    """A grid holds 2^31 - 1 blocks in x: legal options on a matrix that still fits the i32 CSR type can ask for
+    more (4 M rows x 2048 right-hand sides, one column per warp), and such a launch is refused, not truncated."""
+    opts = "spmm-mapping=wave-per-row-tile spmm-tile-size=1 spmm-block-size=32"
+    with pytest.raises(swb.SparseWaveError) as err:
+        swb.launch_shape(opts, rows=4 << 20, nnz=64 << 20, n_rhs=2048)
+    assert err.value.status == _lib.SWB_ERR_UNSUPPORTED and "2147483647" in str(err.value)
+    ok = swb.launch_shape(opts, rows=1 << 20, nnz=16 << 20, n_rhs=2047)
+    assert ok.physical_grid == (1 << 20) * 2047
+    with pytest.raises(swb.SparseWaveError):
+        swb.launch_shape("spmm-mapping=thread-per-output spmm-block-size=32", rows=1 << 30, nnz=1 << 30, n_rhs=128)
+    with pytest.raises(swb.SparseWaveError):
+        swb.launch_shape("spmm-mapping=thread-per-position spmm-block-size=1", rows=8, nnz=1 << 30, n_rhs=4)
+
+
+def test_host_calls_refuse_accumulate_before_anything_else():
+    """accumulate=1 on a host-buffer entry point is refused up front (their result buffer is never read), with or
+    without a context or a device."""
+    lib = _lib.load()
+    o = swb.make_options("spmv-mapping=wave-per-position spmm-mapping=wave-per-row-tile accumulate=1")
+    calls = [lambda: lib.swb_spmv_host(None, C.byref(o), 1, 1, 0, None, None, None, None, None),
+             lambda: lib.swb_spmm_host(None, C.byref(o), 1, 1, 0, 1, None, None, None, None, None),
+             lambda: lib.swb_spmv_resident_host(None, C.byref(o), None, None, None),
+             lambda: lib.swb_spmm_resident_host(None, C.byref(o), None, 1, None, None),
+             lambda: lib.swb_spmv_sharded_host(None, C.byref(o), None, None, None),
+             lambda: lib.swb_spmm_sharded_host(None, C.byref(o), None, 1, None, None)]
+    for call in calls:
+        assert call() == _lib.SWB_ERR_UNSUPPORTED
+        assert b"write-only" in lib.swb_last_error(None)
+
+
+def test_static_status_needs_an_output_pointer():
+    lib = _lib.load()
+    assert lib.swb_bsr16_static_status(None, None) == _lib.SWB_ERR_INVALID_ARGUMENT

@@ -250,3 +250,38 @@ def test_unaligned_operands_take_the_scalar_kernels(ctx):
     big = C1.float().abs() >= 2.0 ** -4 * C1.float().abs().max()
     assert int(((o1 - o2).abs() > 2)[big].sum()) == 0
     assert float((C1.float() - C2.float()).abs().max()) <= 2.0 ** -7 * float(C1.float().abs().max())
+
+
+def test_host_calls_refuse_accumulate_and_sharded_host_without_a_communicator(ctx):
+    """The host-buffer calls never read the caller's result buffer, so accumulate=1 is refused by all of
+    them; the sharded host calls on a context without a communicator are the plain resident operators."""
+    from sparsewave_b200 import SparseWaveError, _lib
+    rp, ci, v = random_csr(900, 700, 8, seed=31)
+    rng = np.random.default_rng(31)
+    x = rng.uniform(-1, 1, 700).astype(np.float32)
+    B = rng.uniform(-1, 1, (700, 8)).astype(np.float32)
+    y, C = np.empty(900, np.float32), np.empty((900, 8), np.float32)
+    acc = "spmv-mapping=wave-per-position spmm-mapping=wave-per-row-tile accumulate=1"
+    resident = ctx.csr_upload(900, 700, rp, ci, v)
+    for call in (lambda: ctx.spmv_host(acc, rp, ci, v, x, y), lambda: ctx.spmm_host(acc, rp, ci, v, B, C),
+                 lambda: resident.spmv_host(acc, x, y), lambda: resident.spmm_host(acc, B, C),
+                 lambda: resident.spmv_sharded_host(acc, x, y), lambda: resident.spmm_sharded_host(acc, B, C)):
+        with pytest.raises(SparseWaveError) as err:
+            call()
+        assert err.value.status == _lib.SWB_ERR_UNSUPPORTED and "write-only" in str(err.value)
+    resident.release()
+    # rows [200, 650) of the matrix, cut and rebased by the library
+    part = ctx.csr_upload_rows(700, rp, ci, v, 200, 650)
+    rows = slice(200, 650)
+    yp, Cp = np.empty(450, np.float32), np.empty((450, 8), np.float32)
+    part.spmv_sharded_host("spmv-mapping=wave-per-position", x, yp)
+    assert_within_bound(yp, oracle.csr_spmv(rp, ci, v, x)[rows], oracle.csr_abs_bound(rp, ci, v, x)[rows])
+    part.spmm_sharded_host("spmm-mapping=wave-per-row-tile spmm-tile-size=8", B, Cp)
+    assert_within_bound(Cp, oracle.csr_spmm(rp, ci, v, B)[rows], oracle.csr_abs_bound(rp, ci, v, B)[rows])
+    part.release()
+    with pytest.raises(SparseWaveError):
+        ctx.csr_upload_rows(700, rp, ci, v, 650, 200)
+    # device operands: without a communicator the sharded operators are the plain ones
+    t = [dev(rp, torch.int32), dev(ci, torch.int32), dev(v), dev(x)]
+    ys = ctx.spmv_sharded("spmv-mapping=wave-per-position", t[0], t[1], t[2], t[3], 700)
+    assert_within_bound(ys.cpu().numpy(), oracle.csr_spmv(rp, ci, v, x), oracle.csr_abs_bound(rp, ci, v, x))

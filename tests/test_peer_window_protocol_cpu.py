@@ -11,9 +11,9 @@ import pytest
 class Rank:
     def __init__(self, ranks, slices):
         self.ready = [0] * ranks
-        self.done = [0] * ranks
+        self.arrivals = 0       # CTAs of any rank whose slice has landed in this window, ever
         self.epoch = 0
-        self.arrived = 0
+        self.count = 0          # CTAs of this rank's current kernel that have finished
         self.data = [[0] * slices for _ in range(ranks)]  # data[source rank][slice] = epoch of the content
 
 
@@ -32,16 +32,14 @@ def exchange_cta(world, r, b, grid):
     dst, piece = b % ranks, b // ranks           # 3. this CTA's slice of the chunk into window dst
     world[dst].data[r][piece] = epoch
     yield
-    me.arrived += 1                              # 4. count the CTA; the last one speaks for the rank
-    if me.arrived != grid:
+    world[dst].arrivals += 1                     # 4. the slice has landed: one arrival at the destination
+    yield
+    me.count += 1                                #    the CTA of this rank that finishes last waits
+    if me.count != grid:
         return
-    for k in range(ranks):
-        world[k].done[r] = epoch
+    while me.arrivals < epoch * grid:            # 5. every rank's CTAs aimed at this window have arrived
         yield
-    for k in range(ranks):                       # 5. every peer's chunk has landed
-        while k != r and me.done[k] < epoch:
-            yield
-    me.arrived = 0
+    me.count = 0
     me.epoch = epoch
 
 
@@ -91,7 +89,7 @@ def test_every_schedule_finishes_and_windows_are_consistent(ranks, slices, resid
             ticks += 1
             assert ticks < 2_000_000, "a schedule did not finish"
         assert not errors, errors[:3]
-        assert all(w.epoch == 5 and w.arrived == 0 for w in world)
+        assert all(w.epoch == 5 and w.count == 0 and w.arrivals == 5 * grid for w in world)
 
 
 def test_the_model_detects_a_missing_ready_wait():

@@ -169,3 +169,76 @@ def test_coo_spmv(ctx, block):
     assert_within_bound(y, oracle.coo_spmv(rows, ri, ci, v, x), bound)
     assert ctx.coo_spmv("", 3, dev(np.zeros(0, np.int32)), dev(np.zeros(0, np.int32)), dev(np.zeros(0, np.float32)),
                         dev(x)).cpu().tolist() == [0, 0, 0]
+
+
+def _offset_view(a, k, dtype):
+    """A CUDA copy of `a` that starts k elements past a 16-byte boundary."""
+    t = torch.empty(len(a) + 4, dtype=dtype, device="cuda")
+    assert t.data_ptr() % 16 == 0
+    t[k:k + len(a)].copy_(torch.as_tensor(np.ascontiguousarray(a)).to(dtype))
+    return t[k:k + len(a)]
+
+
+@pytest.mark.parametrize("k", [1, 2, 3])
+@pytest.mark.parametrize("batch", [3, 16])
+def test_wave_per_position_on_views_off_a_16_byte_boundary(ctx, k, batch):
+    """col and val views that start the same number of elements past a 16-byte boundary (slices of larger
+    arrays, as a row shard cut without a copy is) keep the vectorised span kernel: rows, owning waves and
+    segment ends stay bit-exact, and so does a view whose two arrays are offset differently (scalar kernel)."""
+    rp, ci, v = random_csr(3001, 800, 6, seed=23 + k, empty_fraction=0.35)
+    x = np.random.default_rng(5).uniform(-1, 1, 800).astype(np.float32)
+    opts = f"mapping=wave-per-position wave-position-batch={batch} block-size=128"
+    oy, orow, oworker, oseg = oracle.spmv_wave_position(rp, ci, v, x, block=128, batch=batch, trace=True)
+    bound = oracle.csr_abs_bound(rp, ci, v, x)
+    for kc, kv in ((k, k), (k, (k + 1) % 4)):
+        cv, vv = _offset_view(ci, kc, torch.int32), _offset_view(v, kv, torch.float32)
+        assert cv.data_ptr() % 16 == 4 * kc
+        y, row, worker, seg = ctx.spmv_position_trace(opts, dev(rp, torch.int32), cv, vv, dev(x))
+        assert np.array_equal(row.cpu().numpy(), orow) and np.array_equal(worker.cpu().numpy(), oworker)
+        assert np.array_equal(seg.cpu().numpy(), oseg)
+        assert_within_bound(y.cpu().numpy(), oy, bound)
+        assert_within_bound(ctx.spmv(opts, dev(rp, torch.int32), cv, vv, dev(x)).cpu().numpy(), oy, bound)
+
+
+def test_long_rows_through_shared_memory_bands(ctx, monkeypatch):
+    """The opt-in long-row path of wave-per-position (SWB_BAND_MIN_NNZ): rows of at least 32 positions per
+    band of 32768 columns go through shared-memory bands of x, the span kernel leaves them out.  Power-law
+    rows, a wide matrix with few very long rows and a column count that is no multiple of 4, every row long,
+    and no long row at all."""
+    monkeypatch.setenv("SWB_BAND_MIN_NNZ", "1")
+    cases = [W.zipf_csr(50000, 50000, 1.5, 1, 20000, seed=7, device="cuda"),
+             W.zipf_csr(1200, 1000003, 1.01, 1, 60000, seed=9, device="cuda"),
+             W.uniform_csr(2000, 200000, 3000, seed=11, device="cuda"),
+             W.uniform_csr(400000, 70001, 12, seed=12, device="cuda")]  # each large enough for spans of >= 2 partitions
+    for a in cases:
+        x = W.dense_uniform((a.cols,), seed=8, device="cuda")
+        launches = ctx.kernel_launches
+        y = ctx.spmv("spmv-mapping=wave-per-position spmv-block-size=256", a.row_ptr, a.col_idx, a.values, x)
+        assert ctx.kernel_launches - launches == 4  # long-row list, band boundaries, span kernel, band kernel
+        rp, ci, v = a.numpy()
+        xh = x.cpu().numpy()
+        assert_within_bound(y.cpu().numpy(), oracle.csr_spmv(rp, ci, v, xh, parallel=True),
+                            oracle.csr_abs_bound(rp, ci, v, xh))
+    # accumulate adds to y instead of overwriting it
+    a = cases[0]
+    x = W.dense_uniform((a.cols,), seed=8, device="cuda")
+    y = torch.ones(a.rows, device="cuda")
+    ctx.spmv("spmv-mapping=wave-per-position accumulate=1", a.row_ptr, a.col_idx, a.values, x, y)
+    rp, ci, v = a.numpy()
+    xh = x.cpu().numpy()
+    assert_within_bound(y.cpu().numpy() - 1.0, oracle.csr_spmv(rp, ci, v, xh, parallel=True),
+                        oracle.csr_abs_bound(rp, ci, v, xh) + 1.0)
+    monkeypatch.delenv("SWB_BAND_MIN_NNZ")
+    launches = ctx.kernel_launches
+    ctx.spmv("spmv-mapping=wave-per-position", a.row_ptr, a.col_idx, a.values, x)
+    assert ctx.kernel_launches - launches == 2  # zero fill and span kernel: the path is opt-in
+
+
+def test_gather_probe_adds_every_product(ctx):
+    """swb_probe_stream_gather: the sinks add up to sum val[p] * x[col[p]] over the positions it covers."""
+    a, x = W.config_c3(device="cuda", rows=1 << 16, max_len=2048)
+    sink = ctx.probe_stream_gather(a.col_idx, a.values, x)
+    n = a.nnz - a.nnz % 4
+    want = float((a.values[:n].double() * x[a.col_idx[:n].long()].double()).sum())
+    scale = float((a.values[:n].double() * x[a.col_idx[:n].long()].double()).abs().sum())
+    assert abs(float(sink.double().sum()) - want) <= 1e-5 * scale

@@ -27,20 +27,21 @@ def test_matches_the_context_entry_point_twice_in_a_row(ctx):
         got = api.bsr16_spmm_bf16_static(a.block_row_ptr, a.block_col_idx, a.block_values, B)
         # same kernel, same arithmetic: bit-identical bf16 outputs
         assert torch.equal(got.view(torch.uint16), expected.view(torch.uint16))
-    # asynchronous form (no status read-back), then an explicit synchronisation
+    # asynchronous form (no status read-back in the call): the outcome is asked for afterwards, through the
+    # same fixed array and again without any allocation
     out = torch.empty_like(expected)
     api.bsr16_spmm_bf16_static(a.block_row_ptr, a.block_col_idx, a.block_values, B, out, wait=False)
-    torch.cuda.synchronize()
+    assert api.bsr16_static_status() == 0  # waits for the stream; no CTA of that call gave up
     assert torch.equal(out.view(torch.uint16), expected.view(torch.uint16))
 
 
 def test_rejects_what_exceeds_the_fixed_array():
-    # 4097 block rows x 8 tiles of 128 columns = 32776 CTAs > 32768 status words
+    # 4097 block rows x 8 tiles of 256 columns = 32776 CTAs > 32768 status words
     brp = torch.zeros(4097 + 1, dtype=torch.int32, device="cuda")
     brp[1:] = 1
     bci = torch.zeros(1, dtype=torch.int32, device="cuda")
     bv = torch.zeros(256, dtype=torch.bfloat16, device="cuda")
-    B = torch.zeros((16, 1024), dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros((16, 2048), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(SparseWaveError) as e:
         api.bsr16_spmm_bf16_static(brp, bci, bv, B)
     assert e.value.status == _lib.SWB_ERR_CAPACITY and "at most 32768" in str(e.value)
