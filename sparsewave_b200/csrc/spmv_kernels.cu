@@ -797,8 +797,8 @@ bool band_path_plan(const CsrSpmvArgs &a, int64_t min_nnz, BandPlan *plan) {
 }
 
 size_t band_scratch_bytes(const BandPlan &plan) {
-  // counter (padded), list of long rows, (bands + 1) x cap table of run starts
-  return 256 + (size_t)plan.cap * 4 + (size_t)(plan.bands + 1) * (size_t)plan.cap * 4;
+  // counter (padded), list of long rows, their sampling strides, (bands + 1) x cap table of run brackets
+  return 256 + 2 * (size_t)plan.cap * 4 + (size_t)(plan.bands + 1) * (size_t)plan.cap * 4;
 }
 
 cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64_t batch,
@@ -819,7 +819,7 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   const int shift = span ? (int)(col_off / 4) : 0;
   const bool banded = span && shift == 0 && band && band_scratch && !trace.enabled();
   int long_min = 0;
-  int *count = nullptr, *long_rows = nullptr, *tab = nullptr;
+  int *count = nullptr, *long_rows = nullptr, *strides = nullptr, *tab = nullptr;
   if (banded) {
     // zero fill fused with the search for long rows, then the band boundaries of those rows
     static std::atomic<bool> configured[64];
@@ -834,7 +834,8 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
     long_min = band->long_min;
     count = static_cast<int *>(band_scratch);
     long_rows = count + 64;
-    tab = long_rows + band->cap;
+    strides = long_rows + band->cap;
+    tab = strides + band->cap;
     cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int), s);
     if (e != cudaSuccess) return e;
     int64_t blocks = max1(ceil_div(a.rows, 256));
@@ -842,8 +843,8 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
     find_long_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>(a.y, a.rows, !a.accumulate, a.row_ptr, long_min, band->cap,
                                                           count, long_rows);
     ++*launches;
-    band_bounds_kernel<<<(unsigned)(band->cap < 148 * 64 ? band->cap : 148 * 64), 128, 0, s>>>(
-        a.row_ptr, a.col_idx, band->bands, band->cap, count, long_rows, tab);
+    band_bounds_kernel<<<(unsigned)(band->cap < 148 * 16 ? band->cap : 148 * 16), BOUNDS_THREADS, 0, s>>>(
+        a.row_ptr, a.col_idx, band->bands, band->cap, count, long_rows, tab, strides);
     ++*launches;
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -872,7 +873,7 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || !banded) return e;
   spmv_band_kernel<<<(unsigned)dev.sm_count, BAND_THREADS, BAND_SMEM, s>>>(
-      a.nnz, a.cols, a.col_idx, a.val, a.x, a.y, band->bands, band->cap, count, long_rows, tab);
+      a.nnz, a.cols, a.col_idx, a.val, a.x, a.y, band->bands, band->cap, count, long_rows, tab, strides);
   ++*launches;
   return cudaGetLastError();
 }
