@@ -155,36 +155,67 @@ def read_bsr_binary(path) -> dict:
 
 
 def read_matrix_market(path) -> dict:
-    """Coordinate Matrix Market file -> COO with 0-based indices; `symmetric`
-    and `skew-symmetric` files are expanded, `pattern` entries get value 1
-    (benchmark_utils.py:56-177)."""
-    with Path(path).open("r", encoding="utf-8") as f:
+    """Coordinate Matrix Market file -> entries ordered by (row, column), 0-based; the checks, their order and
+    their messages are those of the reference drivers' reader (benchmark_utils.py:56-177): fields real, integer,
+    pattern (value 1); symmetry general or symmetric (expanded; square only); blank and comment lines skipped
+    anywhere; exactly the expected fields per entry; finite values that fit f32; as many entries as declared.
+    Values stay f64 here (`values64`) for the BSR sums; `values` is their f32 rounding."""
+    import math
+    import struct
+    path = Path(path)
+    with path.open("r", encoding="utf-8") as f:
         header = f.readline().strip().split()
-        if len(header) != 5 or header[0] != "%%MatrixMarket" or header[1] != "matrix":
-            raise ValueError("expected a Matrix Market matrix header")
-        layout, field, symmetry = header[2].lower(), header[3].lower(), header[4].lower()
-        if layout != "coordinate":
-            raise ValueError("only coordinate Matrix Market files are supported")
+        if len(header) != 5 or header[:3] != ["%%MatrixMarket", "matrix", "coordinate"]:
+            raise ValueError(f"{path}: expected a Matrix Market coordinate matrix")
+        field, symmetry = header[3].lower(), header[4].lower()
         if field not in ("real", "integer", "pattern"):
-            raise ValueError(f"unsupported Matrix Market field: {field}")
-        if symmetry not in ("general", "symmetric", "skew-symmetric"):
-            raise ValueError(f"unsupported Matrix Market symmetry: {symmetry}")
-        line = f.readline()
-        while line.startswith("%") or not line.strip():
-            line = f.readline()
-        rows, cols, entries = (int(t) for t in line.split())
-        ri, ci, va = [], [], []
-        for _ in range(entries):
-            parts = f.readline().split()
-            r, c = int(parts[0]) - 1, int(parts[1]) - 1
-            v = 1.0 if field == "pattern" else float(parts[2])
+            raise ValueError(f"{path}: unsupported Matrix Market field '{field}'")
+        if symmetry not in ("general", "symmetric"):
+            raise ValueError(f"{path}: unsupported Matrix Market symmetry '{symmetry}'")
+        size_line = next((ln for ln in f if ln.strip() and not ln.lstrip().startswith("%")), None)
+        if size_line is None:
+            raise ValueError(f"{path}: missing matrix dimensions")
+        try:
+            rows, cols, declared = map(int, size_line.split())
+        except ValueError as error:
+            raise ValueError(f"{path}: invalid matrix dimensions") from error
+        if rows <= 0 or cols <= 0 or declared < 0:
+            raise ValueError(f"{path}: matrix dimensions must be nonnegative")
+        if symmetry == "symmetric" and rows != cols:
+            raise ValueError(f"{path}: a symmetric matrix must be square")
+        entries, read = [], 0
+        expected = 2 if field == "pattern" else 3
+        for line_number, line in enumerate(f, start=3):
+            stripped = line.strip()
+            if not stripped or stripped.startswith("%"):
+                continue
+            parts = stripped.split()
+            if len(parts) != expected:
+                raise ValueError(f"{path}:{line_number}: expected {expected} fields")
+            try:
+                r, c = int(parts[0]) - 1, int(parts[1]) - 1
+                v = 1.0 if field == "pattern" else (float(int(parts[2])) if field == "integer" else float(parts[2]))
+            except ValueError as error:
+                raise ValueError(f"{path}:{line_number}: invalid matrix entry") from error
             if not (0 <= r < rows and 0 <= c < cols):
-                raise ValueError("Matrix Market coordinate is out of bounds")
-            ri.append(r); ci.append(c); va.append(v)
-            if symmetry != "general" and r != c:
-                ri.append(c); ci.append(r); va.append(-v if symmetry == "skew-symmetric" else v)
-    return {"rows": rows, "columns": cols, "row_indices": np.array(ri, np.int32),
-            "column_indices": np.array(ci, np.int32), "values": np.array(va, np.float32)}
+                raise ValueError(f"{path}:{line_number}: matrix index is out of bounds")
+            if not math.isfinite(v):
+                raise ValueError(f"{path}:{line_number}: matrix value must be finite")
+            try:
+                struct.pack("<f", v)
+            except (OverflowError, struct.error) as error:
+                raise ValueError(f"{path}:{line_number}: matrix value must fit in f32") from error
+            entries.append((r, c, v))
+            read += 1
+            if symmetry == "symmetric" and r != c:
+                entries.append((c, r, v))
+    if read != declared:
+        raise ValueError(f"{path}: header declares {declared} entries, but the file contains {read}")
+    entries.sort(key=lambda e: (e[0], e[1]))
+    values64 = np.array([e[2] for e in entries], np.float64)
+    return {"rows": rows, "columns": cols, "row_indices": np.array([e[0] for e in entries], np.int32),
+            "column_indices": np.array([e[1] for e in entries], np.int32), "values": values64.astype(np.float32),
+            "values64": values64}
 
 
 def coo_to_csr(rows: int, row_idx, col_idx, values):
