@@ -160,6 +160,8 @@ int main(int argc, char **argv) {
     swb_options_default(&options);
     checkSwb(ctx, swb_options_parse(ctx, &options, args.options.c_str()), "options");
     checkSwb(ctx, swb_options_validate(ctx, &options), "options");
+    // every dispatch must produce the whole result: with accumulate=1 the timed dispatches would keep adding
+    if (options.accumulate) throw std::runtime_error("options: accumulate=1 is not accepted by the runner");
     checkSwb(ctx, swb_check_csr_host(ctx, (int64_t)m.rows, (int64_t)m.columns, (int64_t)m.nnz, m.rowOffsets.data(),
                                      m.columnIndices.data()),
              "matrix");

@@ -37,3 +37,38 @@ def test_reference_arm_spmm_and_bsr_workloads():
     for workload, kind_key in (("c2", "n_rhs"), ("c5", "nnzb")):
         line = json.loads(_run(workload=workload).splitlines()[-1])
         assert kind_key in line["config"] and line["value"] > 0
+
+
+def test_parity_record_counts_mismatches():
+    """bench.check_parity on CPU tensors: the oracle's own output passes, one corrupted output is counted under
+    both criteria and fails the record; bf16 BSR outputs are held to one ulp of the oracle's bits."""
+    import numpy as np
+    import torch
+
+    import bench
+    import oracle
+    from tests.helpers import random_csr
+    rp, ci, v = random_csr(300, 200, 7, seed=5)
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-1, 1, 200).astype(np.float32)
+    B = rng.uniform(-1, 1, (200, 8)).astype(np.float32)
+    y = torch.from_numpy(oracle.csr_spmv(rp, ci, v, x))
+    rec = bench.check_parity("spmv", rp, ci, v, x, y, block_elems=64)  # several row blocks
+    assert rec["ok"] and rec["checked_rows"] == 300 and rec["mismatches_north_star"] == 0
+    y[17] += 1.0
+    rec = bench.check_parity("spmv", rp, ci, v, x, y)
+    assert not rec["ok"] and rec["mismatches_north_star"] == 1 and rec["mismatches_reference_1e-4"] == 1
+    C = torch.from_numpy(oracle.csr_spmm(rp, ci, v, B))
+    rec = bench.check_parity("spmm", rp, ci, v, B, C, block_elems=256)
+    assert rec["ok"] and rec["checked_outputs"] == 300 * 8
+    from sparsewave_b200 import workloads as W
+    a = W.random_bsr(6, 5, 16, 0.5, seed=3)
+    Bb = W.dense_normal((80, 16), seed=3)
+    operands = (a.block_row_ptr.numpy(), a.block_col_idx.numpy(), a.block_values.view(torch.uint16).numpy(),
+                Bb.view(torch.uint16).numpy())
+    bits, _ = oracle.bsr_spmm_bf16(*operands, 16)
+    good = torch.from_numpy(bits.copy()).view(torch.bfloat16)
+    assert bench.check_parity("bsr", *operands, good)["ok"]
+    bits[3, 5] += 3  # three ulps off
+    rec = bench.check_parity("bsr", *operands, torch.from_numpy(bits).view(torch.bfloat16))
+    assert not rec["ok"] and rec["mismatches_beyond_one_bf16_ulp"] == 1

@@ -208,3 +208,26 @@ def test_full_size_c5_properties(ctx):
         assert_bf16_close(C[b0 * 16:(b0 + 8) * 16], sub, bci[sl], bv[sl.start * 256:sl.stop * 256], Bh, 16)
     # every output was written (no NaN from uninitialised memory) and the checksum matches the f64 total
     assert bool(torch.isfinite(C.float()).all())
+
+
+@pytest.mark.parametrize("rows,band,half,rnd,n", [(5000, 8, 100, 8, 16), (70001, 32, 1024, 32, 64), (3000, 4, 2000, 0, 32),
+                                                  (1025, 0, 1, 6, 48)])
+def test_wave_per_row_tile_with_a_staged_window_of_b(ctx, monkeypatch, rows, band, half, rnd, n):
+    """The opt-in TMA-staged variant of wave-per-row-tile (SWB_SPMM_STAGED=1): 1024 matrix rows x 16 columns per
+    CTA, the rows of B around the diagonal read from shared memory and the others from global memory.  Banded,
+    banded plus random, a band wider than the window, no band at all; row counts that leave a partial last block;
+    the result equals the oracle's whatever falls into the window, and accumulate adds to C."""
+    a = W.banded_random_csr(rows, rows, band, half, rnd, seed=rows, device="cuda")
+    B = W.dense_uniform((rows, n), seed=3, device="cuda")
+    opts = "spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256"
+    monkeypatch.setenv("SWB_SPMM_STAGED", "1")
+    C = ctx.spmm(opts, a.row_ptr, a.col_idx, a.values, B)
+    C2 = torch.ones((rows, n), device="cuda")
+    ctx.spmm(opts + " accumulate=1", a.row_ptr, a.col_idx, a.values, B, C2)
+    monkeypatch.delenv("SWB_SPMM_STAGED")
+    assert ctx.device_status() == 0
+    rp, ci, v = a.numpy()
+    Bh = B.cpu().numpy()
+    want, bound = oracle.csr_spmm(rp, ci, v, Bh, parallel=True), oracle.csr_abs_bound(rp, ci, v, Bh)
+    assert_within_bound(C.cpu().numpy(), want, bound)
+    assert_within_bound(C2.cpu().numpy(), want + 1.0, bound + 1.0)
