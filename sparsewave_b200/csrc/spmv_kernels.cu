@@ -77,6 +77,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 // zero fill (buildOutputInitialization, SparsePositionScheduling.cpp:31-47)
 // ---------------------------------------------------------------------------
 __global__ void fill_zero_kernel(float *__restrict__ y, int64_t n) {
+  // A kernel launched behind this one with programmatic stream serialisation may start its prologue now
+  // (it waits with griddepcontrol.wait before it touches y).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) y[i] = 0.0f;
@@ -859,11 +862,24 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   }
   const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
   const size_t span_smem = (size_t)(block / 32) * SPAN_CHUNK * sizeof(int);
+  // Directly behind this call's own zero fill the span kernel is launched with programmatic stream
+  // serialisation: its row search and first loads overlap the end of the fill, and it waits
+  // (griddepcontrol.wait) before its first addition to y.
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = span_smem;
+  cfg.stream = s;
+  cfg.attrs = pdl;
+  cfg.numAttrs = (!banded && !a.accumulate) ? 1 : 0;
 #define SWB_WPP(TR, MB)                                                                   \
   do {                                                                                    \
     if (span)                                                                             \
-      spmv_wave_span_kernel<TR, MB><<<(unsigned)grid, block, span_smem, s>>>(              \
-          a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace, long_min, shift); \
+      cudaLaunchKernelEx(&cfg, spmv_wave_span_kernel<TR, MB>, a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, \
+                         a.val, a.x, a.y, trace, long_min, shift);                         \
     else                                                                                  \
       spmv_wave_per_position_kernel<TR, MB><<<(unsigned)grid, block, smem, s>>>(           \
           a.rows, a.nnz, waves, batch, a.row_ptr, a.col_idx, a.val, a.x, a.y, trace);      \

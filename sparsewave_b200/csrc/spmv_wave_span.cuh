@@ -124,6 +124,10 @@ __global__ void __launch_bounds__(MAX_BLOCK) spmv_wave_span_kernel(
   int4 cn;
   float4 vn;
   load_chunk(sb & ~3, cn, vn);
+  // Launched behind the zero fill with programmatic stream serialisation, the kernel has come this far
+  // while the fill may still be running: y is touched only after it has finished.  (Without that launch
+  // attribute this returns at once.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   for (int cb = sb & ~3; cb < se; cb += SPAN_CHUNK) {
     const int ce = (cb + SPAN_CHUNK < se) ? cb + SPAN_CHUNK : se;
