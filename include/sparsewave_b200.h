@@ -300,6 +300,24 @@ SWB_API int swb_spmm_resident_host(swb_context *ctx, const swb_options *opts,
                                    const swb_csr_handle *matrix, int64_t n_rhs,
                                    const float *B, float *C);
 
+/* The same for a bf16 BSR matrix: swb_bsr_upload checks the block structure on
+ * the host (offsets start at 0, are monotone and end at nnzb; block columns in
+ * range) and copies it to the device once; swb_bsr_spmm_bf16_resident_host
+ * copies B (cols x n_rhs bf16) in, runs the BSR SpMM (the tensor-core kernel
+ * for 16 x 16 blocks), copies C (rows x n_rhs bf16) out and synchronises. */
+typedef struct swb_bsr_handle swb_bsr_handle;
+SWB_API int swb_bsr_upload(swb_context *ctx, int64_t rows, int64_t cols,
+                           int64_t nnzb, int64_t block_size,
+                           const int32_t *block_row_ptr,
+                           const int32_t *block_col_idx,
+                           const uint16_t *block_values, swb_bsr_handle **out);
+SWB_API void swb_bsr_release(swb_context *ctx, swb_bsr_handle *matrix);
+SWB_API int swb_bsr_spmm_bf16_resident_host(swb_context *ctx,
+                                            const swb_options *opts,
+                                            const swb_bsr_handle *matrix,
+                                            int64_t n_rhs, const uint16_t *B,
+                                            uint16_t *C);
+
 /* ---- sharded operators -------------------------------------------------- */
 /* One row shard per rank of the context's communicator (swb_comm_init), the
  * dense operand owned in equal contiguous chunks of ceil(cols / n_ranks) rows

@@ -95,6 +95,9 @@ SIGNATURES = {
     "swb_csr_upload_rows": (C.c_int, [_CTX, _I64, _I64, _P, _P, _P, _I64, _I64, C.POINTER(C.c_void_p)]),
     "swb_spmv_sharded_host": (C.c_int, [_CTX, _OPT, _P, _P, _P]),
     "swb_spmm_sharded_host": (C.c_int, [_CTX, _OPT, _P, _I64, _P, _P]),
+    "swb_bsr_upload": (C.c_int, [_CTX, _I64, _I64, _I64, _I64, _P, _P, _P, C.POINTER(C.c_void_p)]),
+    "swb_bsr_release": (None, [_CTX, _P]),
+    "swb_bsr_spmm_bf16_resident_host": (C.c_int, [_CTX, _OPT, _P, _I64, _P, _P]),
     "swb_check_csr_host": (C.c_int, [_CTX, _I64, _I64, _I64, _P, _P]),
     "swb_spmv_memref": (C.c_int, [_CTX, _OPT, _P, _P, _P, _P, _P, _P]),
     "swb_spmm_memref": (C.c_int, [_CTX, _OPT, _P, _P, _P, _P, _P, _P]),

@@ -368,6 +368,17 @@ class Context:
                                                   C.byref(h)))
         return ResidentCsr(self, h, int(row_end - row_begin), int(cols))
 
+    def bsr_upload(self, cols: int, block_row_ptr, block_col_idx, block_values, block_size: int) -> "ResidentBsr":
+        """Checks and copies a host bf16 BSR matrix to the device once; returns a handle for
+        `ResidentBsr.spmm_host` (B in, C out per call)."""
+        rows = (len(block_row_ptr) - 1) * block_size
+        h = C.c_void_p()
+        self._check(self._lib.swb_bsr_upload(self._ctx, rows, int(cols), len(block_col_idx), int(block_size),
+                                             _host_ptr(block_row_ptr, torch.int32, "block_row_ptr"),
+                                             _host_ptr(block_col_idx, torch.int32, "block_col_idx"),
+                                             _host_ptr(block_values, torch.bfloat16, "block_values"), C.byref(h)))
+        return ResidentBsr(self, h, rows, int(cols))
+
     def check_csr_host(self, rows, cols, row_ptr, col_idx) -> None:
         self._check(self._lib.swb_check_csr_host(self._ctx, rows, cols, len(col_idx),
                                                  _host_ptr(row_ptr, torch.int32, "row_ptr"),
@@ -412,6 +423,25 @@ class ResidentCsr:
     def release(self) -> None:
         if self._h:
             self.ctx._lib.swb_csr_release(self.ctx._ctx, self._h)
+            self._h = None
+
+
+class ResidentBsr:
+    """A bf16 BSR matrix kept on the device by `Context.bsr_upload`."""
+
+    def __init__(self, ctx: Context, handle, rows: int, cols: int):
+        self.ctx, self._h, self.rows, self.cols = ctx, handle, rows, cols
+
+    def spmm_host(self, options, B, C_out):
+        o = self.ctx._opts(options)
+        self.ctx._check(self.ctx._lib.swb_bsr_spmm_bf16_resident_host(self.ctx._ctx, C.byref(o), self._h, int(B.shape[1]),
+                                                                      _host_ptr(B, torch.bfloat16, "B"),
+                                                                      _host_ptr(C_out, torch.bfloat16, "C")))
+        return C_out
+
+    def release(self) -> None:
+        if self._h:
+            self.ctx._lib.swb_bsr_release(self.ctx._ctx, self._h)
             self._h = None
 
 

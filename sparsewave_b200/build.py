@@ -70,10 +70,13 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose, extra), srcs))
     if _stale(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-lcuda"]
+        # linked under another name and renamed: a reader never sees a half-written library
+        fresh = LIB.with_suffix(".so.new")
+        cmd = [_nvcc(), "-shared", "-o", str(fresh), *map(str, objs), "-lcudart", "-lcuda"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
+        os.replace(fresh, LIB)
     build_runner(verbose)
     build_loaders(verbose)
     return LIB

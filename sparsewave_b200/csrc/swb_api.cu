@@ -1247,6 +1247,88 @@ int swb_spmm_resident_host(swb_context *ctx, const swb_options *o, const swb_csr
                             });
 }
 
+// ---- device-resident bf16 BSR matrix, host dense operands ---------------------------------------
+
+struct swb_bsr_handle {
+  int64_t rows = 0, cols = 0, nnzb = 0, block_size = 0;
+  int32_t *block_row_ptr = nullptr, *block_col_idx = nullptr;
+  uint16_t *block_values = nullptr;
+};
+
+int swb_bsr_upload(swb_context *ctx, int64_t rows, int64_t cols, int64_t nnzb, int64_t bs, const int32_t *brp,
+                   const int32_t *bci, const uint16_t *bv, swb_bsr_handle **out) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (!out) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr upload: out is NULL");
+  *out = nullptr;
+  st = check_bsr(ctx, rows, cols, nnzb, bs, 1);
+  if (st != SWB_OK) return st;
+  if (!brp || (nnzb > 0 && (!bci || !bv))) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr upload: NULL operand pointer");
+  const int64_t brows = rows / bs, bcols = cols / bs;
+  if (brp[0] != 0) return fail(ctx, SWB_ERR_INVALID_DATA, "block-row offsets must start at 0, but got %d", brp[0]);
+  for (int64_t r = 0; r < brows; ++r)
+    if (brp[r + 1] < brp[r])
+      return fail(ctx, SWB_ERR_INVALID_DATA, "block-row offsets must be non-decreasing, but block row %lld has %d > %d",
+                  (long long)r, brp[r], brp[r + 1]);
+  if (brp[brows] != nnzb)
+    return fail(ctx, SWB_ERR_INVALID_DATA, "last block-row offset must equal the number of blocks, but got %d and %lld",
+                brp[brows], (long long)nnzb);
+  for (int64_t b = 0; b < nnzb; ++b)
+    if (bci[b] < 0 || bci[b] >= bcols)
+      return fail(ctx, SWB_ERR_INVALID_DATA, "block column %d of block %lld is out of bounds for %lld block columns", bci[b],
+                  (long long)b, (long long)bcols);
+  swb_bsr_handle *h = new swb_bsr_handle();
+  h->rows = rows; h->cols = cols; h->nnzb = nnzb; h->block_size = bs;
+  const size_t value_bytes = (size_t)nnzb * bs * bs * 2;
+  cudaError_t e = cudaMalloc(&h->block_row_ptr, (size_t)(brows + 1) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&h->block_col_idx, (size_t)(nnzb > 0 ? nnzb : 1) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&h->block_values, value_bytes > 0 ? value_bytes : 16);
+  if (e == cudaSuccess) e = cudaMemcpy(h->block_row_ptr, brp, (size_t)(brows + 1) * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && nnzb > 0) e = cudaMemcpy(h->block_col_idx, bci, (size_t)nnzb * 4, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && nnzb > 0) e = cudaMemcpy(h->block_values, bv, value_bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    swb_bsr_release(ctx, h);
+    return cuda_fail(ctx, e, "bsr upload");
+  }
+  *out = h;
+  return SWB_OK;
+}
+
+void swb_bsr_release(swb_context *ctx, swb_bsr_handle *h) {
+  if (!h) return;
+  if (ctx) cudaSetDevice(ctx->device);
+  cudaFree(h->block_row_ptr); cudaFree(h->block_col_idx); cudaFree(h->block_values);
+  delete h;
+}
+
+int swb_bsr_spmm_bf16_resident_host(swb_context *ctx, const swb_options *o, const swb_bsr_handle *h, int64_t n_rhs,
+                                    const uint16_t *B, uint16_t *C) {
+  int st = check_ctx(ctx);
+  if (st != SWB_OK) return st;
+  if (!o) return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "options is NULL");
+  if (n_rhs < 1) return fail(ctx, SWB_ERR_INVALID_SHAPE, "bsr_spmm: right-hand side must have at least one column, but got %lld", (long long)n_rhs);
+  if (!h || (h->cols > 0 && !B) || (h->rows > 0 && !C))
+    return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "bsr_spmm: NULL matrix handle or operand pointer");
+  st = ensure_host_stream(ctx);
+  if (st != SWB_OK) return st;
+  const size_t b_bytes = (size_t)h->cols * n_rhs * 2, c_bytes = (size_t)h->rows * n_rhs * 2;
+  st = workspace_reserve(ctx, pad256(b_bytes) + pad256(c_bytes));
+  if (st != SWB_OK) return st;
+  uint16_t *d_B = workspace_take<uint16_t>(ctx, h->cols * n_rhs);
+  uint16_t *d_C = workspace_take<uint16_t>(ctx, h->rows * n_rhs);
+  cudaStream_t s = ctx->host_stream;
+  if (b_bytes > 0) SWB_CUDA(ctx, cudaMemcpyAsync(d_B, B, b_bytes, cudaMemcpyHostToDevice, s));
+  st = swb_bsr_spmm_bf16(ctx, o, h->rows, h->cols, h->nnzb, h->block_size, n_rhs, h->block_row_ptr, h->block_col_idx,
+                         h->block_values, d_B, d_C, s);
+  cudaError_t e = cudaSuccess;
+  if (st == SWB_OK && c_bytes > 0) e = cudaMemcpyAsync(C, d_C, c_bytes, cudaMemcpyDeviceToHost, s);
+  const cudaError_t e1 = cudaStreamSynchronize(s);  // also after an error: the copies touch caller memory
+  if (st != SWB_OK) return st;
+  if (e == cudaSuccess) e = e1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "bsr resident host call");
+  return SWB_OK;
+}
+
 // ---- sharded operators: gather the dense operand, then the local kernel -----------------------
 
 extern "C++" {

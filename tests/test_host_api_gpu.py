@@ -285,3 +285,29 @@ def test_host_calls_refuse_accumulate_and_sharded_host_without_a_communicator(ct
     t = [dev(rp, torch.int32), dev(ci, torch.int32), dev(v), dev(x)]
     ys = ctx.spmv_sharded("spmv-mapping=wave-per-position", t[0], t[1], t[2], t[3], 700)
     assert_within_bound(ys.cpu().numpy(), oracle.csr_spmv(rp, ci, v, x), oracle.csr_abs_bound(rp, ci, v, x))
+
+
+def test_resident_bsr_with_host_operands(ctx):
+    """swb_bsr_upload + swb_bsr_spmm_bf16_resident_host: the block structure is checked and copied once, a call
+    sends B and returns C; the result equals the device-operand call's bit for bit, and a malformed structure
+    is refused at upload."""
+    from sparsewave_b200 import workloads as W
+    a = W.random_bsr(40, 30, 16, 0.2, seed=21)
+    B = W.dense_normal((30 * 16, 64), seed=21)
+    resident = ctx.bsr_upload(a.cols, a.block_row_ptr, a.block_col_idx, a.block_values, 16)
+    C_host = torch.empty((a.rows, 64), dtype=torch.bfloat16)
+    for _ in range(2):
+        resident.spmm_host("", B, C_host)
+        C_dev = ctx.bsr_spmm("", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(), B.cuda(), 16)
+        assert torch.equal(C_host.view(torch.uint16), C_dev.cpu().view(torch.uint16))
+    assert ctx.device_status() == 0
+    resident.release()
+    bad = a.block_col_idx.clone()
+    bad[3] = 30  # one block column past the end
+    with pytest.raises(SparseWaveError) as err:
+        ctx.bsr_upload(a.cols, a.block_row_ptr, bad, a.block_values, 16)
+    assert err.value.status == _lib.SWB_ERR_INVALID_DATA and "out of bounds" in str(err.value)
+    short = a.block_row_ptr.clone()
+    short[-1] -= 1
+    with pytest.raises(SparseWaveError, match="last block-row offset"):
+        ctx.bsr_upload(a.cols, short, a.block_col_idx, a.block_values, 16)
