@@ -786,6 +786,46 @@ def run_e2e(args, env, wl, options, shard, steps):
             "timer": timer}
 
 
+# Configuration 3 names three mappings to compare; the line carries them beside the headline mapping.
+C3_MAPPINGS = [
+    "spmv-mapping=thread-per-position spmv-position-chunk-size=8 spmv-position-reduction=segmented spmv-block-size=256",
+    "spmv-mapping=thread-per-position spmv-block-size=256",
+    "spmv-mapping=block-per-row spmv-block-size=64",
+    "spmv-mapping=wave-per-row spmv-block-size=128",
+]
+
+
+def compare_mappings(env, option_strings, steps=10):
+    """The other SpMV mappings on configuration 3: a few timed steps each and the same parity check."""
+    import torch
+
+    from sparsewave_b200 import make_options
+    ctx, device = env["ctx"], env["device"]
+    wl = build_workload("c3", device, None)
+    a, x = wl["a"], wl["dense"]
+    hc = host_copies(wl)
+    y = torch.empty(a.rows, dtype=torch.float32, device=device)
+    out = []
+    for text in option_strings:
+        opts = make_options(text)
+        call = lambda: ctx.spmv(opts, a.row_ptr, a.col_idx, a.values, x, y)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        parity = check_parity("spmv", hc["row_ptr"], hc["col_idx"], hc["values"], hc["dense"], y)
+        out.append({"options": text, "steps": steps, "ms_per_step": ms, "value": wl["bytes"] / (ms * 1e-3) / 1e9,
+                    "unit": "GB/s", "launch": "host launch per step",
+                    "parity": {k: parity[k] for k in ("checked_rows", "mismatches_north_star", "max_err_over_bound", "ok")}})
+    return out
+
+
 def write_results(args, records, line):
     """results.jsonl (one line per finished configuration, appended) and metadata.json: the sweep files of the
     reference runner (benchmark/benchmark_utils.py:1018-1059 in the SparseWave tree) in JSON form."""
@@ -817,7 +857,13 @@ def run_ours(args):
     clocks.__enter__()
     rec = measure_workload(args, env, headline, headline=True, steps_arg=args.steps, warmup=args.warmup, clocks=clocks)
     records = [rec]
+    mappings = None
     if default_command and world == 1 and not args.no_configs:
+        try:
+            mappings = compare_mappings(env, C3_MAPPINGS)
+        except Exception as exc:  # noqa: BLE001
+            mappings = [{"failed": repr(exc), "parity": {"ok": False}}]
+        torch.cuda.empty_cache()
         for name in ("c1", "c2", "c4", "c5"):
             try:
                 records.append(measure_workload(args, env, name, headline=False, steps_arg=None, warmup=3))
@@ -840,6 +886,7 @@ def run_ours(args):
 
     bad = [r["workload"] for r in records
            if r.get("device_status", 0) != 0 or (r.get("parity") is not None and not r["parity"].get("ok", False))]
+    bad += ["c3 with " + m.get("options", "?") for m in (mappings or []) if not m["parity"].get("ok", False)]
     if rank == 0:
         line = {
             "metric": METRIC, "value": rec["value"], "unit": "GB/s", "n_gpus": world, "steps": rec["steps"],
@@ -866,6 +913,8 @@ def run_ours(args):
                         "cpu_baseline", "library_baseline", "e2e", "gpu_launches", "device_status", "l2", "launch",
                         "failed")
                 line["configs"] = [{k: r[k] for k in keep if k in r} for r in records[1:]]
+            if mappings is not None:
+                line["mappings"] = mappings  # the other SpMV mappings on the headline matrix
         if bad:
             line["void"] = "output mismatch or device status in: " + "; ".join(bad)
         print(json.dumps(line), flush=True)

@@ -771,10 +771,10 @@ cudaError_t launch_spmv_thread_per_position(const CsrSpmvArgs &a, int block, int
 int64_t wave_per_position_auto_batch(int64_t nnz, int block, const DeviceInfo &dev) {
   // Spans long enough that the one row search per span is amortised, short enough that the warps fill the
   // SMs many times over.  Measured on a power-law SpMV: 92 M nonzeros want 32 to 48 partitions per span
-  // (0.397 ms; 0.400 at 64, 0.413 at 16), an eighth of it (11.5 M) wants 8 to 16 (0.062 ms; 0.066 at 9).
-  // Small problems keep at least 16 warps per SM.
+  // (0.397 ms; 0.400 at 64, 0.413 at 16), a quarter of it 12 to 16 (0.110 ms; 0.115 at 9), an eighth 8 (0.059 ms;
+  // 0.065 at 4, 0.062 at 16).  Small problems keep at least 16 warps per SM.
   const int64_t waves = wave_position_wave_count(nnz, block);
-  int64_t batch = waves / ((int64_t)dev.sm_count * 64 * 8);
+  int64_t batch = waves / ((int64_t)dev.sm_count * 64 * 6);
   if (batch > 48) batch = 48;
   if (batch < 8) {
     const int64_t by_occupancy = waves / ((int64_t)dev.sm_count * 16);
