@@ -239,6 +239,11 @@ __global__ void __launch_bounds__(THREADS) bsr16_spmm_tcgen05_kernel(
   done_ok = __syncthreads_and(done_ok);
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (!done_ok && tid == 0) atomicExch(status + (PER_CTA_STATUS ? blockIdx.x : 0), 1);
+  if (!done_ok || failed) {
+    // A wait gave up with copies or MMAs of this CTA possibly still in flight: give them a bounded time (1 ms)
+    // to land before the shared memory and the TMEM columns go back to the SM.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
 
   if (done_ok && !failed && warp < 4) {
     // TMEM lane m of accumulator h = column n0 + 128 h + m of C; this warp reads lanes 32 warp .. +32

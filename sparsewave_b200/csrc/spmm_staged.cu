@@ -86,6 +86,9 @@ __global__ void __launch_bounds__(STAGED_THREADS, 1) spmm_row_block_staged_kerne
   }
   if (!__syncthreads_and(ok)) {  // bounded wait ran out: the window is not valid
     if (tid == 0) atomicExch(status, 5);
+    // copies of this CTA may still be in flight: a bounded time (1 ms) for them to land before the shared
+    // memory goes back to the SM
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     return;
   }
 
