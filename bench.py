@@ -557,7 +557,7 @@ def measure_workload(args, env, name, *, headline, steps_arg, warmup, clocks=Non
         phases = {}
         try:
             if getattr(ctx, "window", None) is not None:
-                gather = lambda: ctx.window_allgather(owned)
+                gather = lambda: ctx.window_allgather_next(owned)  # the form the sharded step uses
             else:
                 chunk = sharding.dense_chunk(a.cols, world)
                 send = torch.zeros((chunk,) + tuple(dense.shape[1:]), dtype=dense.dtype, device=device)

@@ -496,9 +496,11 @@ SWB_API void swb_comm_destroy(swb_context *ctx);
 /* The same exchange as one kernel of peer stores over NVLink instead of
  * ncclAllGather.  swb_comm_window_create (collective over the communicator's
  * ranks, which must be processes of one node) allocates a window of n_ranks *
- * bytes_per_rank bytes on every rank, maps the windows of the other ranks with
- * CUDA IPC and returns this rank's window; bytes_per_rank must be a multiple
- * of 16.  swb_comm_window_allgather queues one kernel on `stream` that stores
+ * bytes_per_rank bytes on every rank (and a second buffer of the same size
+ * behind it, which the sharded operators fill in turn with the first so that
+ * their steps need no "no longer reading" round trip between the ranks), maps
+ * the windows of the other ranks with CUDA IPC and returns this rank's window;
+ * bytes_per_rank must be a multiple of 16.  swb_comm_window_allgather queues one kernel on `stream` that stores
  * the bytes_per_rank bytes at `send` (16-byte aligned device memory) into
  * every rank's window at offset rank * bytes_per_rank; work queued behind it
  * on the same stream finds the whole window filled.  A window must not be read
@@ -506,6 +508,14 @@ SWB_API void swb_comm_destroy(swb_context *ctx);
  * waits on the other ranks are bounded: if one gives up (a rank that never
  * launches its step), swb_device_status reports 3 or 4 and the window content
  * is not valid.  One window per context; capturable in a CUDA graph.
+ * swb_comm_window_allgather_next is the form the sharded operators use: it
+ * fills the window's two buffers in turn (the first call after creation fills
+ * the one swb_comm_window_create returned, the second buffer lies n_ranks *
+ * bytes_per_rank bytes behind it) and stores the address of the buffer of this
+ * call in *gathered.  Calls that take turns need no round trip between the
+ * ranks before the stores; a call that meets the buffer of the call before it
+ * (swb_comm_window_allgather twice, or a replayed graph with an odd number of
+ * steps) waits for the peers first, decided on the device.
  * swb_comm_window_destroy is collective too (every rank unmaps before any
  * rank frees), so call it on every rank, while all ranks are still alive;
  * swb_destroy never runs a collective: on a context that still has a window
@@ -515,6 +525,9 @@ SWB_API int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank,
                                    void **window);
 SWB_API int swb_comm_window_allgather(swb_context *ctx, const void *send,
                                       swb_stream stream);
+SWB_API int swb_comm_window_allgather_next(swb_context *ctx, const void *send,
+                                           swb_stream stream,
+                                           const void **gathered);
 SWB_API void swb_comm_window_destroy(swb_context *ctx);
 
 /* ---- multi-GPU row sharding --------------------------------------------- */

@@ -118,6 +118,7 @@ SIGNATURES = {
     "swb_shard_rows_by_nnz": (C.c_int, [_CTX, _P, _I64, _I64, _P]),
     "swb_comm_window_create": (C.c_int, [_CTX, _I64, C.POINTER(C.c_void_p)]),
     "swb_comm_window_allgather": (C.c_int, [_CTX, _P, _P]),
+    "swb_comm_window_allgather_next": (C.c_int, [_CTX, _P, _P, C.POINTER(C.c_void_p)]),
     "swb_comm_window_destroy": (None, [_CTX]),
     "swb_plan_row_panels": (C.c_int, [_I64, _I64, _P, _I64, _P]),
 }

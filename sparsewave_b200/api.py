@@ -84,7 +84,7 @@ class Context:
 
     def close(self) -> None:
         if self._ctx:
-            self.window = None
+            self.window = self.window_buffers = None
             self._lib.swb_destroy(self._ctx)
             self._ctx = C.c_void_p()
 
@@ -158,16 +158,19 @@ class Context:
     # -- all-gather as one kernel of peer stores (processes of one node) ---------------
     def window_create(self, bytes_per_rank: int) -> torch.Tensor:
         """Collective over the communicator's ranks: allocates this rank's window of comm_world *
-        bytes_per_rank bytes, maps the other ranks' windows and returns a uint8 tensor over the local one."""
+        bytes_per_rank bytes, maps the other ranks' windows and returns a uint8 tensor over the local one.
+        `window_buffers` is a (2, comm_world * bytes_per_rank) view of it and of the second buffer behind it,
+        which the sharded operators fill in turn."""
         ptr = C.c_void_p()
         self._check(self._lib.swb_comm_window_create(self._ctx, int(bytes_per_rank), C.byref(ptr)))
         self.window_bytes_per_rank = int(bytes_per_rank)
 
         class _Window:  # device memory owned by the library, exposed through the CUDA array interface
-            __cuda_array_interface__ = {"shape": (int(bytes_per_rank) * self.comm_world,), "typestr": "|u1",
+            __cuda_array_interface__ = {"shape": (2, int(bytes_per_rank) * self.comm_world), "typestr": "|u1",
                                         "data": (int(ptr.value), False), "version": 3, "strides": None}
 
-        self.window = torch.as_tensor(_Window(), device=torch.device("cuda", self.device))
+        self.window_buffers = torch.as_tensor(_Window(), device=torch.device("cuda", self.device))
+        self.window = self.window_buffers[0]
         return self.window
 
     def window_allgather(self, send: torch.Tensor) -> torch.Tensor:
@@ -180,10 +183,21 @@ class Context:
         self._check(self._lib.swb_comm_window_allgather(self._ctx, send.data_ptr(), self._stream()))
         return self.window
 
+    def window_allgather_next(self, send: torch.Tensor) -> torch.Tensor:
+        """The same exchange into the window's two buffers in turn (no round trip between the ranks before the
+        stores when calls take turns); returns the buffer that this call fills."""
+        if getattr(self, "window", None) is None:
+            raise ValueError("the context has no window (window_create)")
+        if not (send.is_cuda and send.is_contiguous()) or send.numel() * send.element_size() != self.window_bytes_per_rank:
+            raise ValueError("send must be a contiguous CUDA tensor of window_bytes_per_rank bytes")
+        where = C.c_void_p()
+        self._check(self._lib.swb_comm_window_allgather_next(self._ctx, send.data_ptr(), self._stream(), C.byref(where)))
+        return self.window_buffers[0 if where.value == self.window_buffers.data_ptr() else 1]
+
     def window_destroy(self) -> None:
         """Collective: unmaps the peers' windows and frees this rank's."""
         if getattr(self, "window", None) is not None:
-            self.window = None
+            self.window = self.window_buffers = None
             self._lib.swb_comm_window_destroy(self._ctx)
 
     def validate(self, options) -> None:

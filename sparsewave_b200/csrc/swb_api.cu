@@ -1380,10 +1380,11 @@ int gather_dense_operand(swb_context *ctx, const float *owned, bool owned_on_hos
   int64_t window_bytes = 0;
   void *window = swb::peer_window_data(ctx, &window_bytes);
   if (window && window_bytes == (int64_t)chunk_bytes && chunk_bytes % 16 == 0) {
-    int st = swb::window_allgather_and_fill(ctx, send, zero, zero_count, s);
+    const void *gathered = nullptr;  // the two buffers of the window take turns: no ready-flag round trip
+    int st = swb::window_allgather_and_fill(ctx, send, zero, zero_count, s, true, &gathered);
     if (st != SWB_OK) return st;
     if (zero && zero_filled) *zero_filled = true;
-    *full_out = static_cast<const float *>(window);
+    *full_out = static_cast<const float *>(gathered);
     return SWB_OK;
   }
   int st = grow(ctx, &ctx->shard_full, &ctx->shard_full_bytes, chunk_bytes * (size_t)ranks, "cudaMalloc(gathered operand)");

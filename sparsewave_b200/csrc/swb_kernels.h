@@ -141,7 +141,8 @@ void *context_peer_window(const swb_context *ctx);
 void set_context_peer_window(swb_context *ctx, void *window);
 void *peer_window_data(const swb_context *ctx, int64_t *bytes_per_rank);  // NULL without a window
 // swb_comm_window_allgather whose kernel also zero-fills zero[0 .. zero_count) (NULL: no fill)
-int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, int64_t zero_count, cudaStream_t stream);
+int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, int64_t zero_count, cudaStream_t stream,
+                              bool alternate, const void **gathered);
 void abandon_peer_window(swb_context *ctx);  // non-collective tear-down (swb_peer_window.cu)
 int *context_status_flag(const swb_context *ctx);
 void count_launch(swb_context *ctx);

@@ -1,17 +1,24 @@
 // All-gather of the dense operand as one kernel of peer stores over NVLink.
 //
-// Every rank owns a window: a device allocation of [4 KiB header][n_ranks * bytes_per_rank data] exported to
-// the other ranks of the node with CUDA IPC (the handles travel through the context's NCCL communicator at
-// set-up).  A step is one kernel per rank that
-//   1. tells every peer "I no longer read my window" (ready flag, epoch-numbered; stream order guarantees
-//      that the kernel that consumed the previous epoch has finished),
-//   2. waits until every peer has said the same, so no window is overwritten while it is read,
-//   3. stores its own chunk into every rank's window (plain 16-byte peer stores; its own window included);
-//      each CTA serves one destination,
+// Every rank owns a window: a device allocation of [4 KiB header][2 buffers of n_ranks * bytes_per_rank data]
+// exported to the other ranks of the node with CUDA IPC (the handles travel through the context's NCCL
+// communicator at set-up).  A step names the buffer it fills and is one kernel per rank that
+//   1. only when the step before it filled the same buffer: tells every peer "I no longer read my window"
+//      (ready flag, epoch-numbered; stream order guarantees that the kernel that consumed the previous epoch
+//      has finished) and
+//   2. waits until every peer has said the same, so no buffer is overwritten while it is read,
+//   3. stores its own chunk into that buffer of every rank's window (plain 16-byte peer stores; its own
+//      window included); each CTA serves one destination,
 //   4. per CTA: once its stores are ordered system-wide (one fence by one thread behind a CTA barrier), adds
 //      one to the destination's arrival counter with a remote atomic,
-//   5. the CTA of this rank that finishes last waits until this rank's own counter shows the arrivals of
-//      every rank's CTAs for this epoch, so that the kernel after it finds the window complete.
+//   5. the CTA of this rank that finishes last waits until this rank's own counter for that buffer shows
+//      the arrivals of every rank's CTAs for this fill, so that the kernel after it finds the buffer complete.
+// Steps that alternate between the two buffers need neither 1 nor 2: a rank starts epoch e only after its
+// kernel of epoch e - 1 has seen every rank's arrivals of epoch e - 1, and a rank sends those only after (in
+// its stream) the consumer of epoch e - 2 has finished, which was the last reader of the buffer that epoch e
+// fills.  The sharded operators alternate; swb_comm_window_allgather always fills buffer 0 and therefore
+// always takes steps 1 and 2.  Which of the two happens is decided on the device from the header (the
+// buffer of the previous step), so that a replayed CUDA graph with an odd number of steps stays correct.
 // Optionally the kernel also zero-fills an output vector (the separate fill launch of the position
 // mappings) while it would otherwise wait.
 // All waits poll counters in this GPU's own memory that the other ranks write, are bounded, and give up
@@ -33,13 +40,15 @@ namespace {
 
 constexpr int kMaxRanks = 16;
 constexpr int64_t kHeaderBytes = 4096;
-// header words: ready[rank] at 0, arrivals (of all ranks' CTAs, ever) at 256, epoch at 512, local CTA count at 516
-constexpr int kReadyOff = 0, kArrivalsOff = 256, kEpochOff = 512, kCountOff = 516;
+// header words: ready[rank] at 0, arrivals[buffer] (of all ranks' CTAs, ever) at 256, epoch at 512, local CTA count
+// at 516, 1 + the buffer of the last finished step at 520 (0: none yet), finished steps per buffer at 524
+constexpr int kReadyOff = 0, kArrivalsOff = 256, kEpochOff = 512, kCountOff = 516, kLastBufferOff = 520, kFillsOff = 524;
 constexpr unsigned kPollLimit = 1u << 24;  // polls of a word in local memory, 100 ns apart (a few seconds), before giving up
 constexpr int kGridTarget = 256;           // CTAs of a step, split evenly over the destination ranks
 
 struct PeerWindow {
   int ranks = 1, rank = 0, slices = 1;
+  int next_buffer = 0;  // of the alternating (internal) steps
   int64_t bytes_per_rank = 0;
   char *local = nullptr;
   char *peer[kMaxRanks] = {};
@@ -57,28 +66,35 @@ __device__ bool wait_word(const volatile unsigned *word, unsigned target) {
 
 __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restrict__ send, int64_t n16,
                                                              char *const *__restrict__ peer, int rank, int ranks,
-                                                             int64_t bytes_per_rank, float *__restrict__ zero,
-                                                             int64_t zero_count, int *status) {
+                                                             int64_t bytes_per_rank, int buffer,
+                                                             float *__restrict__ zero, int64_t zero_count,
+                                                             int *status) {
   char *local = peer[rank];
   __shared__ unsigned s_epoch;
   __shared__ int s_failed;
   __shared__ int s_last;
+  __shared__ int s_same;
+  __shared__ unsigned s_fill;
   if (threadIdx.x == 0) {
     s_epoch = *reinterpret_cast<volatile unsigned *>(local + kEpochOff) + 1u;
+    s_fill = reinterpret_cast<volatile unsigned *>(local + kFillsOff)[buffer] + 1u;  // this is the n-th fill of the buffer
+    // the step before this one filled the same buffer: its readers have to be waited for (steps 1 and 2)
+    s_same = *reinterpret_cast<volatile unsigned *>(local + kLastBufferOff) == (unsigned)buffer + 1u;
     s_failed = 0;
     s_last = 0;
   }
   __syncthreads();
   const unsigned epoch = s_epoch;
+  const bool handshake = s_same != 0;
 
   // 1. ready flags out (one CTA is enough)
-  if (blockIdx.x == 0 && threadIdx.x < ranks)
+  if (handshake && blockIdx.x == 0 && threadIdx.x < ranks)
     reinterpret_cast<volatile unsigned *>(peer[threadIdx.x] + kReadyOff)[rank] = epoch;
   // the zero fill of the consumer's output rides along while the flags travel
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < zero_count; i += (int64_t)gridDim.x * blockDim.x)
     zero[i] = 0.0f;
   // 2. ready flags in (every CTA looks for itself)
-  if (threadIdx.x < ranks && threadIdx.x != rank &&
+  if (handshake && threadIdx.x < ranks && threadIdx.x != rank &&
       !wait_word(reinterpret_cast<volatile unsigned *>(local + kReadyOff) + threadIdx.x, epoch))
     s_failed = 1;
   __syncthreads();
@@ -87,7 +103,7 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restr
   // After a failed wait the stores still go out (they stay inside the windows) so that the counters below
   // remain consistent; the status word tells the host that the result is not to be trusted.
   const int dst = blockIdx.x % ranks, slice = blockIdx.x / ranks, slices = gridDim.x / ranks;
-  int4 *out = reinterpret_cast<int4 *>(peer[dst] + kHeaderBytes + (int64_t)rank * bytes_per_rank);
+  int4 *out = reinterpret_cast<int4 *>(peer[dst] + kHeaderBytes + ((int64_t)buffer * ranks + rank) * bytes_per_rank);
   const int64_t stride = (int64_t)slices * blockDim.x;
   int64_t i = (int64_t)slice * blockDim.x + threadIdx.x;
   for (; i + 3 * stride < n16; i += 4 * stride) {
@@ -102,7 +118,7 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restr
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
-    atomicAdd_system(reinterpret_cast<unsigned *>(peer[dst] + kArrivalsOff), 1u);
+    atomicAdd_system(reinterpret_cast<unsigned *>(peer[dst] + kArrivalsOff) + buffer, 1u);
     const unsigned before = atomicAdd(reinterpret_cast<unsigned *>(local + kCountOff), 1u);
     s_last = before == gridDim.x - 1;
     if (s_failed) atomicExch(status, 3);
@@ -110,11 +126,16 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restr
   __syncthreads();
   if (!s_last) return;
 
-  // 5. every rank's CTAs aimed at this rank (slices per rank, so gridDim.x per epoch) have arrived
+  // 5. every rank's CTAs aimed at this rank (slices per rank, so gridDim.x per fill) have arrived.  The
+  //    arrivals are counted per buffer: a rank that is one step ahead already adds to the other buffer's
+  //    counter, and none can be two steps ahead (it would need this rank's arrivals of the step between).
   if (threadIdx.x == 0) {
-    if (!wait_word(reinterpret_cast<volatile unsigned *>(local + kArrivalsOff), epoch * gridDim.x)) atomicExch(status, 4);
+    if (!wait_word(reinterpret_cast<volatile unsigned *>(local + kArrivalsOff) + buffer, s_fill * gridDim.x))
+      atomicExch(status, 4);
     __threadfence_system();
+    reinterpret_cast<volatile unsigned *>(local + kFillsOff)[buffer] = s_fill;
     *reinterpret_cast<volatile unsigned *>(local + kCountOff) = 0u;
+    *reinterpret_cast<volatile unsigned *>(local + kLastBufferOff) = (unsigned)buffer + 1u;
     *reinterpret_cast<volatile unsigned *>(local + kEpochOff) = epoch;
   }
 }
@@ -185,7 +206,7 @@ int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **wind
   PeerWindow *w = new PeerWindow();
   w->ranks = ranks; w->rank = rank; w->bytes_per_rank = bytes_per_rank;
   w->slices = kGridTarget / ranks > 0 ? kGridTarget / ranks : 1;
-  const size_t total = (size_t)kHeaderBytes + (size_t)ranks * (size_t)bytes_per_rank;
+  const size_t total = (size_t)kHeaderBytes + 2 * (size_t)ranks * (size_t)bytes_per_rank;  // header, two buffers
   struct Slot { cudaIpcMemHandle_t handle; int ok; int pad[3]; };  // one exchanged record, 80 bytes
   Slot *d_slots = nullptr;  // [0, ranks): gathered, [ranks]: this rank's
   Slot mine, all[kMaxRanks];
@@ -258,7 +279,11 @@ int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **wind
 }
 
 int swb_comm_window_allgather(swb_context *ctx, const void *send, swb_stream stream) {
-  return swb::window_allgather_and_fill(ctx, send, nullptr, 0, static_cast<cudaStream_t>(stream));
+  return swb::window_allgather_and_fill(ctx, send, nullptr, 0, static_cast<cudaStream_t>(stream), false, nullptr);
+}
+
+int swb_comm_window_allgather_next(swb_context *ctx, const void *send, swb_stream stream, const void **gathered) {
+  return swb::window_allgather_and_fill(ctx, send, nullptr, 0, static_cast<cudaStream_t>(stream), true, gathered);
 }
 
 }  // extern "C"
@@ -267,7 +292,11 @@ namespace swb {
 
 // The exchange of swb_comm_window_allgather; the same kernel also stores `zero_count` zeros at `zero`
 // (the output vector of the operator that consumes the window), or nothing when zero is NULL.
-int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, int64_t zero_count, cudaStream_t stream) {
+// alternate: fill the buffer that the previous alternating call did not (no ready-flag round trip between
+// such calls), else buffer 0, the one swb_comm_window_create returned.  *gathered (if not NULL): where the
+// gathered operand of this call lies.
+int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, int64_t zero_count, cudaStream_t stream,
+                              bool alternate, const void **gathered) {
   if (!ctx) {
     set_thread_error("context is NULL");
     return SWB_ERR_INVALID_ARGUMENT;
@@ -280,9 +309,12 @@ int window_allgather_and_fill(swb_context *ctx, const void *send, float *zero, i
   if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "cudaSetDevice", cudaGetErrorString(e));
   // enough 16-byte loads in flight (16 KiB per CTA) to keep the NVLink egress busy whatever the rank count;
   // the grid is the same on every rank and for every step of a window (the arrival count relies on it)
+  const int buffer = alternate ? w->next_buffer : 0;
+  if (alternate) w->next_buffer ^= 1;
+  if (gathered) *gathered = w->local + kHeaderBytes + (int64_t)buffer * w->ranks * w->bytes_per_rank;
   peer_allgather_kernel<<<(unsigned)(w->ranks * w->slices), 256, 0, stream>>>(
       static_cast<const int4 *>(send), w->bytes_per_rank / 16, w->d_peer, w->rank, w->ranks, w->bytes_per_rank,
-      zero, zero ? zero_count : 0, context_status_flag(ctx));
+      buffer, zero, zero ? zero_count : 0, context_status_flag(ctx));
   count_launch(ctx);
   e = cudaGetLastError();
   if (e != cudaSuccess) return window_fail(ctx, SWB_ERR_CUDA, "window all-gather launch", cudaGetErrorString(e));

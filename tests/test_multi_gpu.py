@@ -41,14 +41,44 @@ def _rank_main(rank, world, port):
         bound = oracle.csr_abs_bound(rp, ci, v, xh)[rows]
         assert np.all(np.abs(y - oracle.csr_spmv(rp, ci, v, xh)[rows]) <= 1e-5 * bound + 1e-30)
         # the library's own all-gather: one kernel of peer stores into an IPC window, several steps in a row
-        # with a different x each (a step must not overwrite a window that a peer still reads)
+        # with a different x each (a step must not overwrite a buffer that a peer still reads); the operator's
+        # steps fill the window's two buffers in turn
         ctx.window_create(sharding.window_bytes(a.cols, world))
-        for step in range(4):
+        for step in range(5):
             xs = x * float(step + 1)
             y4 = op.spmv(xs[lo:hi].contiguous()).cpu().numpy()
             want = oracle.csr_spmv(rp, ci, v, xh * np.float32(step + 1))[rows]
             assert np.all(np.abs(y4 - want) <= 1e-5 * (step + 1) * bound + 1e-30)
-            assert torch.equal(ctx.window.view(torch.float32)[:a.cols], xs)
+            assert torch.equal(ctx.window_buffers[step & 1].view(torch.float32)[:a.cols], xs)
+        # a captured graph of three steps replayed: its first step fills the buffer that its last one filled
+        # (the kernel sees that on the device and waits for the peers' readers), then plain steps again, and a
+        # direct all-gather (always the first buffer) in between
+        xg = x[lo:hi].clone()
+        yg = torch.empty(shard.rows, device="cuda")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(3):
+                    op.spmv(xg, yg)
+        torch.cuda.current_stream().wait_stream(side)
+        for replay in range(3):
+            xg.copy_(x[lo:hi] * float(replay + 2))
+            graph.replay()
+            want = oracle.csr_spmv(rp, ci, v, xh * np.float32(replay + 2))[rows]
+            assert np.all(np.abs(yg.cpu().numpy() - want) <= 1e-5 * (replay + 2) * bound + 1e-30)
+        got = ctx.window_allgather(x[lo:hi].contiguous() if (hi - lo) * 4 == ctx.window_bytes_per_rank else
+                                   torch.nn.functional.pad(x[lo:hi], (0, ctx.window_bytes_per_rank // 4 - (hi - lo))))
+        assert torch.equal(got.view(torch.float32)[:a.cols], x)
+        seen = set()
+        for k in range(3):  # the alternating form, called directly: the returned buffer holds this call's gather
+            got = ctx.window_allgather_next((x[lo:hi] * float(k + 7)).contiguous())
+            assert torch.equal(got.view(torch.float32)[:a.cols], x * float(k + 7))
+            seen.add(got.data_ptr())
+        assert len(seen) == 2
+        y5 = op.spmv(x[lo:hi].contiguous()).cpu().numpy()
+        assert np.all(np.abs(y5 - y) <= 1e-5 * bound + 1e-30)
         assert ctx.device_status() == 0
         ctx.window_destroy()
         ctx.window_create(sharding.window_bytes(a.cols, world, (8,)))
