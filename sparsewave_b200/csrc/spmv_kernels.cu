@@ -862,9 +862,9 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   }
   const size_t smem = (size_t)(block / 32) * TILE_POS * sizeof(int);
   const size_t span_smem = (size_t)(block / 32) * SPAN_CHUNK * sizeof(int);
-  // Directly behind this call's own zero fill the span kernel is launched with programmatic stream
-  // serialisation: its row search and first loads overlap the end of the fill, and it waits
-  // (griddepcontrol.wait) before its first addition to y.
+  // Directly behind this call's own zero fill (or the library's exchange kernel, which fills y too) the
+  // span kernel is launched with programmatic stream serialisation: its row search and first loads
+  // overlap the end of that kernel, and it waits (griddepcontrol.wait) before it reads x or adds to y.
   cudaLaunchAttribute pdl[1];
   pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   pdl[0].val.programmaticStreamSerializationAllowed = 1;
@@ -874,7 +874,7 @@ cudaError_t launch_spmv_wave_per_position(const CsrSpmvArgs &a, int block, int64
   cfg.dynamicSmemBytes = span_smem;
   cfg.stream = s;
   cfg.attrs = pdl;
-  cfg.numAttrs = (!banded && !a.accumulate) ? 1 : 0;
+  cfg.numAttrs = (!banded && (!a.accumulate || a.behind_exchange)) ? 1 : 0;
 #define SWB_WPP(TR, MB)                                                                   \
   do {                                                                                    \
     if (span)                                                                             \

@@ -40,6 +40,7 @@ struct swb_context {
   // size, and the gathered operand when no peer window serves (both grown on demand, kept).
   char *shard_send = nullptr, *shard_full = nullptr;
   size_t shard_send_bytes = 0, shard_full_bytes = 0;
+  bool behind_exchange = false;  // one-shot: the next swb_spmv is queued directly behind the exchange kernel
   void *comm = nullptr;        // NCCL communicator of the multi-GPU path (swb_comm.cu)
   void *peer_window = nullptr; // peer-store all-gather window (swb_peer_window.cu)
   int comm_ranks = 1, comm_rank = 0;
@@ -568,6 +569,8 @@ static int spmv_impl(swb_context *ctx, const swb_options *o, int64_t rows, int64
     return fail(ctx, SWB_ERR_UNSUPPORTED, "accumulate is available for the position mappings of SpMV only");
   swb::CsrSpmvArgs a{rows, cols, nnz, row_ptr, col_idx, val, x, y};
   a.accumulate = o->accumulate != 0;
+  a.behind_exchange = ctx->behind_exchange && a.accumulate;
+  ctx->behind_exchange = false;
   const int B = (int)o->block_size;
   cudaError_t e = cudaSuccess;
   switch (o->mapping) {
@@ -1415,7 +1418,10 @@ int swb_spmv_sharded(swb_context *ctx, const swb_options *o, int64_t rows, int64
   if (!filled) return swb_spmv(ctx, o, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
   swb_options add = *o;
   add.accumulate = 1;
-  return swb_spmv(ctx, &add, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
+  ctx->behind_exchange = true;  // nothing was queued between the exchange kernel and this call's kernel
+  st = swb_spmv(ctx, &add, rows, cols, nnz, row_ptr, col_idx, val, x, y, stream);
+  ctx->behind_exchange = false;
+  return st;
 }
 
 int swb_spmm_sharded(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols, int64_t nnz, int64_t n_rhs,
@@ -1454,10 +1460,12 @@ static int sharded_host_call(swb_context *ctx, const swb_options *o, const swb_c
   st = gather_dense_operand(ctx, owned_host, true, h->cols, width, s, &dense, wants_fill ? d_out : nullptr, h->rows, &filled);
   swb_options local = *o;
   if (filled) local.accumulate = 1;
+  ctx->behind_exchange = filled && spmv;  // the kernel of swb_spmv comes directly behind the exchange kernel
   if (st == SWB_OK)
     st = spmv ? swb_spmv(ctx, &local, h->rows, h->cols, h->nnz, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense, d_out, s)
               : swb_spmm(ctx, &local, h->rows, h->cols, h->nnz, width, h->whole.row_ptr, h->whole.col_idx, h->whole.val, dense,
                          d_out, s);
+  ctx->behind_exchange = false;
   cudaError_t e = cudaSuccess;
   if (st == SWB_OK && out_bytes > 0) e = cudaMemcpyAsync(out_host, d_out, out_bytes, cudaMemcpyDeviceToHost, s);
   const cudaError_t e1 = cudaStreamSynchronize(s);  // also after an error: the copies touch caller memory

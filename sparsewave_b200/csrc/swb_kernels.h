@@ -16,6 +16,10 @@ struct CsrSpmvArgs {
   const float *x;
   float *y;
   bool accumulate = false;  // add to y instead of overwriting (position mappings: no zero fill)
+  // The kernel queued directly before this call on the same stream is the library's own exchange kernel,
+  // which produced x and the zeros of y and releases its dependents early: the span kernel may then be
+  // launched with programmatic stream serialisation (it reads neither x nor y before its wait).
+  bool behind_exchange = false;
 };
 
 struct CsrSpmmArgs {

@@ -86,6 +86,9 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const int4 *__restr
   __syncthreads();
   const unsigned epoch = s_epoch;
   const bool handshake = s_same != 0;
+  // A kernel launched behind this one with programmatic stream serialisation (the span kernel of the sharded
+  // SpMV) may start its prologue now; it waits for the end of this grid before it reads x or touches y.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // 1. ready flags out (one CTA is enough)
   if (handshake && blockIdx.x == 0 && threadIdx.x < ranks)
