@@ -57,7 +57,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the full workload size,
 # from the one-pass ncu captures summarised under profiles/ (None where no capture exists).
-NCU_TRAFFIC_BYTES = {"c2": 18.1e6, "c3": 0.7934e9, "c4": 16.71e9, "c5": 45.3e6}
+NCU_TRAFFIC_BYTES = {"c2": 18.1e6, "c3": 0.7934e9, "c4": 16.69e9, "c5": 45.3e6}
 
 
 def parse_args():
