@@ -302,6 +302,73 @@ __global__ void spmm_wave_per_row_fused_kernel(int64_t rows, int64_t N, const in
   }
 }
 
+// Rows of B of 128 * R floats (R = 2, 3, 4): the same fusion with the whole warp on one position; a lane
+// holds R float4 of the row of C (columns 4 * lane + 128 * r) and reads the position's row of B as R
+// coalesced 512-byte runs.  Two positions are in flight for R = 2, one for wider rows (as many bytes per
+// lane as in the kernel above).
+template <int R>
+__global__ void spmm_wave_per_row_wide_kernel(int64_t rows, int64_t N, const int32_t *__restrict__ row_ptr,
+                                              const int32_t *__restrict__ col, const float *__restrict__ val,
+                                              const float *__restrict__ B, float *__restrict__ C,
+                                              bool accumulate) {
+  constexpr int U = R == 2 ? 2 : 1;  // positions in flight
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  const float4 *Bt = reinterpret_cast<const float4 *>(B) + lane;
+  const int64_t N4 = N / 4;
+  float4 acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto fma4 = [&](float4 &a, float v, const float4 &b) {
+    a.x = add(a.x, mul(v, b.x)); a.y = add(a.y, mul(v, b.y));
+    a.z = add(a.z, mul(v, b.z)); a.w = add(a.w, mul(v, b.w));
+  };
+  int cn = start + lane < end ? __ldg(col + start + lane) : 0;
+  float vn = start + lane < end ? __ldg(val + start + lane) : 0.0f;
+  for (int base = start; base < end; base += 32) {
+    const int cl = cn;
+    const float vl = vn;
+    const int mine = base + 32 + lane;
+    cn = mine < end ? __ldg(col + mine) : 0;
+    vn = mine < end ? __ldg(val + mine) : 0.0f;
+    const int left = end - base < 32 ? end - base : 32;
+    int j = 0;
+    for (; j + U <= left; j += U) {
+      float4 b[U][R];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float4 *brow = Bt + (int64_t)__shfl_sync(FULL, cl, j + u) * N4;
+#pragma unroll
+        for (int r = 0; r < R; ++r) b[u][r] = __ldg(brow + 32 * r);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float v = __shfl_sync(FULL, vl, j + u);
+#pragma unroll
+        for (int r = 0; r < R; ++r) fma4(acc[r], v, b[u][r]);
+      }
+    }
+    if (U > 1 && j < left) {  // U == 2: one position left over
+      const float4 *brow = Bt + (int64_t)__shfl_sync(FULL, cl, j) * N4;
+      const float v = __shfl_sync(FULL, vl, j);
+#pragma unroll
+      for (int r = 0; r < R; ++r) fma4(acc[r], v, __ldg(brow + 32 * r));
+    }
+  }
+  float4 *out = reinterpret_cast<float4 *>(C + row * N) + lane;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float4 a = acc[r];
+    if (accumulate) {
+      const float4 old = out[32 * r];
+      a.x = add(old.x, a.x); a.y = add(old.y, a.y); a.z = add(old.z, a.z); a.w = add(old.w, a.w);
+    }
+    out[32 * r] = a;
+  }
+}
+
 // Short matrix rows with rows of B of up to 32 floats: a full warp per row leaves most lanes with one
 // position or none and the kernel waits on three dependent loads per warp.  Here L = 4, 8 or 16 lanes
 // serve one matrix row (32/L rows per warp): G = N/4 adjacent lanes cover the row of B with one float4
@@ -469,6 +536,16 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
   // warp, or by part of a warp where the rows are short.
   const int64_t N = a.n_rhs;
   const bool pow2_row = N >= 4 && N <= 128 && (N & (N - 1)) == 0;
+  if ((N == 256 || N == 384 || N == 512) && aligned16(a.B) && aligned16(a.C)) {
+    SWB_GRID(grid, ceil_div(a.rows, block / 32));
+    if (N == 256)
+      spmm_wave_per_row_wide_kernel<2><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
+    else if (N == 384)
+      spmm_wave_per_row_wide_kernel<3><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
+    else
+      spmm_wave_per_row_wide_kernel<4><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
+    return cudaGetLastError();
+  }
   if (pow2_row && aligned16(a.B) && aligned16(a.C)) {
     if (N == 4) return launch_row_of_tiles<1>(a, block, s);
     if (N == 8) return launch_row_of_tiles<2>(a, block, s);
@@ -495,6 +572,7 @@ int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs
   // Mirrors launch_spmm_wave_per_row_tile and launch_row_of_tiles for 16-byte aligned operands.
   const int64_t wpb = block / 32;
   const bool pow2_row = n_rhs >= 4 && n_rhs <= 128 && (n_rhs & (n_rhs - 1)) == 0;
+  if (n_rhs == 256 || n_rhs == 384 || n_rhs == 512) return max1(ceil_div(rows, wpb));
   if (!pow2_row) return max1(ceil_div(rows * ceil_div(n_rhs, tile), wpb));
   if (n_rhs > 32) return max1(ceil_div(rows, wpb));
   const int64_t G = n_rhs / 4, mean = rows > 0 ? nnz / rows : 0;

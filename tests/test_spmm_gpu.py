@@ -33,7 +33,7 @@ def test_runtime_goldens(ctx, opts, g):
 
 
 @pytest.mark.parametrize("tile", [1, 2, 3, 4, 5, 8, 12, 16, 31, 32])
-@pytest.mark.parametrize("n", [1, 4, 7, 24, 32, 48, 64, 70, 96, 128, 256])
+@pytest.mark.parametrize("n", [1, 4, 7, 24, 32, 48, 64, 70, 96, 128, 256, 384, 512])
 def test_wave_per_row_tile_all_tiles(ctx, tile, n):
     rp, ci, v = random_csr(701, 433, 20, seed=tile * 100 + n, empty_fraction=0.15)
     B = np.random.default_rng(4).uniform(-1, 1, (433, n)).astype(np.float32)
