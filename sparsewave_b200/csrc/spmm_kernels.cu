@@ -188,6 +188,43 @@ __global__ void spmm_wave_per_row_tile_vec_kernel(int64_t rows, int64_t N, int64
   const float *Bt = B + j0 + 4 * cq;
 
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if constexpr (G >= 4) {
+    // 32 positions per pass, read by the whole warp with one coalesced load of col and one of val and
+    // handed to the lane groups by shuffles (see the fused-row kernel below); same order of additions
+    auto fma4 = [&](float v, const float4 &b) {
+      acc.x = add(acc.x, mul(v, b.x)); acc.y = add(acc.y, mul(v, b.y));
+      acc.z = add(acc.z, mul(v, b.z)); acc.w = add(acc.w, mul(v, b.w));
+    };
+    int cn = start + lane < end ? __ldg(col + start + lane) : 0;
+    float vn = start + lane < end ? __ldg(val + start + lane) : 0.0f;
+    for (int base = start; base < end; base += 32) {
+      const int cl = cn;
+      const float vl = vn;
+      const int mine = base + 32 + lane;
+      cn = mine < end ? __ldg(col + mine) : 0;
+      vn = mine < end ? __ldg(val + mine) : 0.0f;
+      const int left = end - base < 32 ? end - base : 32;
+      int j = 0;
+      for (; j + 4 * PG <= left; j += 4 * PG) {
+        const int k = j + pg;
+        const int c0 = __shfl_sync(FULL, cl, k), c1 = __shfl_sync(FULL, cl, k + PG);
+        const int c2 = __shfl_sync(FULL, cl, k + 2 * PG), c3 = __shfl_sync(FULL, cl, k + 3 * PG);
+        const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+        const float4 b1 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c1 * N));
+        const float4 b2 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c2 * N));
+        const float4 b3 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c3 * N));
+        const float v0 = __shfl_sync(FULL, vl, k), v1 = __shfl_sync(FULL, vl, k + PG);
+        const float v2 = __shfl_sync(FULL, vl, k + 2 * PG), v3 = __shfl_sync(FULL, vl, k + 3 * PG);
+        fma4(v0, b0); fma4(v1, b1); fma4(v2, b2); fma4(v3, b3);
+      }
+      for (; j < left; j += PG) {
+        const int kk = j + pg;
+        const int c0 = __shfl_sync(FULL, cl, kk & 31);
+        const float v0 = __shfl_sync(FULL, vl, kk & 31);
+        if (kk < left) fma4(v0, __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N)));
+      }
+    }
+  } else {
   int p = start + pg;
   for (; p + PG < end; p += 2 * PG) {
     const int c0 = __ldg(col + p), c1 = __ldg(col + p + PG);
@@ -205,6 +242,7 @@ __global__ void spmm_wave_per_row_tile_vec_kernel(int64_t rows, int64_t N, int64
     const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
     acc.x = add(acc.x, mul(v0, b0.x)); acc.y = add(acc.y, mul(v0, b0.y));
     acc.z = add(acc.z, mul(v0, b0.z)); acc.w = add(acc.w, mul(v0, b0.w));
+  }
   }
 
   // distance 16: lanes with bit 4 set keep (z, w), the others (x, y)
