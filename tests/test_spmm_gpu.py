@@ -132,6 +132,19 @@ def test_bsr_f32_is_bit_exact(ctx, bs):
     assert np.array_equal(C.cpu().numpy(), expected)
 
 
+@pytest.mark.parametrize("bs,n", [(4, 32), (16, 64), (32, 96), (48, 32), (33, 64)])
+def test_bsr_f32_rows_shared_by_a_warp_are_bit_exact(ctx, bs, n):
+    """N a multiple of 32: a warp's outputs share the block row's values (one load, passed on by shuffles);
+    block sizes below, at and above the warp width, and one that is no power of two."""
+    a = W.random_bsr(20, 17, bs, 0.3, seed=bs + n, dtype=torch.float32)
+    B = W.dense_uniform((17 * bs, n), seed=bs)
+    C = ctx.bsr_spmm("spmm-block-size=128", a.block_row_ptr.cuda(), a.block_col_idx.cuda(), a.block_values.cuda(),
+                     B.cuda(), bs)
+    expected = oracle.bsr_spmm_f32(a.block_row_ptr.numpy(), a.block_col_idx.numpy(), a.block_values.numpy(),
+                                   B.numpy(), bs)
+    assert np.array_equal(C.cpu().numpy(), expected)
+
+
 def _bsr_bf16_case(ctx, grid_rows, grid_cols, bs, n, density, seed):
     a = W.random_bsr(grid_rows, grid_cols, bs, density, seed=seed)
     B = W.dense_normal((grid_cols * bs, n), seed=seed)
@@ -145,6 +158,8 @@ def _bsr_bf16_case(ctx, grid_rows, grid_cols, bs, n, density, seed):
 @pytest.mark.parametrize("bs", [4, 8, 16, 32])
 def test_bsr_bf16(ctx, bs):
     _bsr_bf16_case(ctx, 24, 20, bs, 24, 0.25, seed=bs)
+    if bs != 16:  # (16 is the tensor-core kernel) rows shared by a warp
+        _bsr_bf16_case(ctx, 24, 20, bs, 64, 0.25, seed=bs + 1)
 
 
 @pytest.mark.parametrize("n", [8, 64, 128, 200, 512])
