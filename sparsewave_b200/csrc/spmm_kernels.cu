@@ -315,6 +315,14 @@ __global__ void spmm_wave_per_row_fused_kernel(int64_t rows, int64_t N, const in
       const float v2 = __shfl_sync(FULL, vl, k + 2 * PG), v3 = __shfl_sync(FULL, vl, k + 3 * PG);
       fma4(v0, b0); fma4(v1, b1); fma4(v2, b2); fma4(v3, b3);
     }
+    for (; j + 2 * PG <= left; j += 2 * PG) {  // short rows and row ends: two rows of B in flight
+      const int k = j + pg;
+      const int c0 = __shfl_sync(FULL, cl, k), c1 = __shfl_sync(FULL, cl, k + PG);
+      const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+      const float4 b1 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c1 * N));
+      const float v0 = __shfl_sync(FULL, vl, k), v1 = __shfl_sync(FULL, vl, k + PG);
+      fma4(v0, b0); fma4(v1, b1);
+    }
     // the ragged end of the pass: every lane takes part in the shuffles, only lanes with a position add
     for (; j < left; j += PG) {
       const int kk = j + pg;
@@ -536,13 +544,21 @@ cudaError_t launch_subwarp(const CsrSpmmArgs &a, int block, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-// Lanes per matrix row for rows of B of 4*G floats: enough lane groups that each gets about four of the
-// mean row's positions, at least 4 lanes (and at least G), at most the warp.
+// Lanes per matrix row for rows of B of 4*G floats: at least 4 lanes (and at least G), at most the warp,
+// doubled while a lane group would get more than positions_per_lane_group(G) of the mean row's positions.
+// The figures are measured (1 M and 2 M rows, uniform columns, 2 to 64 positions per row): few lanes per row
+// mean more rows in flight per warp and fewer butterfly steps, and win until the per-group chain of
+// positions gets long.  Against four positions per group for every width: N = 8, 24 per row 0.226 -> 0.125 ms;
+// N = 16, 24 per row 0.492 -> 0.205 ms; N = 32, 10 per row 0.514 -> 0.246 ms; N = 64, 5 per row (half a warp
+// instead of a warp) 1.02 -> 0.53 ms.
+constexpr int64_t positions_per_lane_group(int G) { return G == 1 ? 6 : G == 2 ? 12 : G <= 8 ? 16 : 12; }
+
 template <int G>
 cudaError_t launch_row_of_tiles(const CsrSpmmArgs &a, int block, cudaStream_t s) {
   const int64_t mean = a.rows > 0 ? a.nnz / a.rows : 0;
   int lanes = G > 4 ? G : 4;
-  while (lanes < 32 && (int64_t)(lanes / G) * 4 < mean) lanes *= 2;
+  constexpr int64_t kPerGroup = positions_per_lane_group(G);
+  while (lanes < 32 && (int64_t)(lanes / G) * kPerGroup < mean) lanes *= 2;
   if constexpr (G <= 4) if (lanes == 4) return launch_subwarp<G, 4>(a, block, s);
   if constexpr (G <= 8) if (lanes == 8) return launch_subwarp<G, 8>(a, block, s);
   if (lanes == 16) return launch_subwarp<G, 16>(a, block, s);
@@ -551,8 +567,9 @@ cudaError_t launch_row_of_tiles(const CsrSpmmArgs &a, int block, cudaStream_t s)
     spmm_wave_per_row_fused_kernel<G><<<grid, block, 0, s>>>(a.rows, a.n_rhs, a.row_ptr, a.col_idx, a.val, a.B, a.C,
                                                              a.accumulate);
     return cudaGetLastError();
+  } else {
+    return launch_tile<4 * G>(a, block, 4 * G, s);
   }
-  return launch_tile<4 * G>(a, block, 4 * G, s);
 }
 
 }  // namespace
@@ -589,13 +606,10 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
     if (N == 8) return launch_row_of_tiles<2>(a, block, s);
     if (N == 16) return launch_row_of_tiles<4>(a, block, s);
     if (N == 32) return launch_row_of_tiles<8>(a, block, s);
+    if (N == 64) return launch_row_of_tiles<16>(a, block, s);  // half a warp per row where rows are short
     SWB_GRID(grid, ceil_div(a.rows, block / 32));
-    if (N == 64)
-      spmm_wave_per_row_fused_kernel<16><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,
-                                                                 a.accumulate);
-    else
-      spmm_wave_per_row_fused_kernel<32><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,
-                                                                 a.accumulate);
+    spmm_wave_per_row_fused_kernel<32><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C,
+                                                               a.accumulate);
     return cudaGetLastError();
   }
   if (tile <= 1) return launch_tile<1>(a, block, tile, s);
@@ -612,10 +626,10 @@ int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs
   const bool pow2_row = n_rhs >= 4 && n_rhs <= 128 && (n_rhs & (n_rhs - 1)) == 0;
   if (n_rhs == 256 || n_rhs == 384 || n_rhs == 512) return max1(ceil_div(rows, wpb));
   if (!pow2_row) return max1(ceil_div(rows * ceil_div(n_rhs, tile), wpb));
-  if (n_rhs > 32) return max1(ceil_div(rows, wpb));
+  if (n_rhs > 64) return max1(ceil_div(rows, wpb));
   const int64_t G = n_rhs / 4, mean = rows > 0 ? nnz / rows : 0;
   int64_t lanes = G > 4 ? G : 4;
-  while (lanes < 32 && (lanes / G) * 4 < mean) lanes *= 2;
+  while (lanes < 32 && (lanes / G) * positions_per_lane_group((int)G) < mean) lanes *= 2;
   return max1(ceil_div(ceil_div(rows, 32 / lanes), wpb));
 }
 

@@ -41,10 +41,10 @@ def test_wave_per_row_tile_all_tiles(ctx, tile, n):
     assert_within_bound(C, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
 
 
-@pytest.mark.parametrize("mean_len", [2, 9, 30, 90])
-@pytest.mark.parametrize("n", [4, 8, 16, 32])
+@pytest.mark.parametrize("mean_len", [2, 9, 14, 30, 90])
+@pytest.mark.parametrize("n", [4, 8, 16, 32, 64])
 def test_wave_per_row_tile_short_rows(ctx, mean_len, n):
-    """Rows of B of up to 32 floats: the lanes that serve one matrix row (4, 8, 16 or the whole warp) follow
+    """Rows of B of up to 64 floats: the lanes that serve one matrix row (4, 8, 16 or the whole warp) follow
     the mean row length; row counts that do not fill the last warp, one row, and accumulation."""
     for rows in (701, 1):
         rp, ci, v = random_csr(rows, 433, mean_len, seed=mean_len * 10 + n, empty_fraction=0.1)
