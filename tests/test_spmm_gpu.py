@@ -37,8 +37,15 @@ def test_runtime_goldens(ctx, opts, g):
 def test_wave_per_row_tile_all_tiles(ctx, tile, n):
     rp, ci, v = random_csr(701, 433, 20, seed=tile * 100 + n, empty_fraction=0.15)
     B = np.random.default_rng(4).uniform(-1, 1, (433, n)).astype(np.float32)
-    C = run(ctx, f"spmm-mapping=wave-per-row-tile spmm-tile-size={tile} spmm-block-size=64", rp, ci, v, B)
-    assert_within_bound(C, oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B))
+    opts = f"spmm-mapping=wave-per-row-tile spmm-tile-size={tile} spmm-block-size=64"
+    want, bound = oracle.csr_spmm(rp, ci, v, B), oracle.csr_abs_bound(rp, ci, v, B)
+    C = run(ctx, opts, rp, ci, v, B)
+    assert_within_bound(C, want, bound)
+    if tile == 32 and n >= 96:  # the kernels for wide rows of B also add to an existing C
+        Cd = torch.full((701, n), 2.0, dtype=torch.float32, device="cuda")
+        ctx.spmm(opts + " accumulate=1", dev(rp, torch.int32), dev(ci, torch.int32), dev(v, torch.float32),
+                 dev(B, torch.float32), Cd)
+        assert_within_bound(Cd.cpu().numpy(), want + 2.0, bound + 2.0)
 
 
 @pytest.mark.parametrize("mean_len", [2, 9, 14, 30, 90])
