@@ -690,6 +690,10 @@ int swb_spmm(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL operand pointer");
   if (o->accumulate && o->spmm_mapping == SWB_THREAD_PER_OUTPUT)
     return fail(ctx, SWB_ERR_UNSUPPORTED, "accumulate is not available for the thread-per-output SpMM mapping");
+  // The wave kernels step through a row's positions in 32-bit strides of up to 128 past its end.
+  if (o->spmm_mapping == SWB_WAVE_PER_ROW_TILE && nnz > kI32Max - 256)
+    return fail(ctx, SWB_ERR_UNSUPPORTED, "spmm: the wave-per-row-tile mapping supports at most %lld nonzeros, but got %lld",
+                (long long)(kI32Max - 256), (long long)nnz);
   swb_launch_shape shape;
   st = swb_launch_shape_query(ctx, o, rows, nnz, n_rhs, &shape);  // refuses grids beyond the CUDA limit
   if (st != SWB_OK) return st;
@@ -1641,7 +1645,7 @@ int swb_bundle_launch(swb_context *ctx, const char *operation, int64_t n, void *
   o.spmm_mapping = SWB_WAVE_PER_ROW_TILE;
   o.spmm_block_size = 64;
   o.spmm_tile_size = 4;
-  return swb_spmm(ctx, &o, n, kI32Max, kI32Max, 4, static_cast<const int32_t *>(args[0]),
+  return swb_spmm(ctx, &o, n, kI32Max, kI32Max - 256, 4, static_cast<const int32_t *>(args[0]),
                   static_cast<const int32_t *>(args[1]), static_cast<const float *>(args[2]),
                   static_cast<const float *>(args[3]), static_cast<float *>(args[4]), stream);
 }

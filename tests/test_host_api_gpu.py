@@ -111,6 +111,16 @@ def test_argument_errors(ctx):
     before = ctx.kernel_launches
     ctx.spmv("mapping=wave-per-position", *t)
     assert ctx.kernel_launches == before + 2  # zero fill + compute
+    # declared sizes at the edge of the i32 range are refused before anything is launched: the wave kernels
+    # step through positions in 32-bit strides past a row's end
+    B = torch.zeros((4, 4), device="cuda")
+    out = torch.zeros((5, 4), device="cuda")
+    o = make_options("spmm-mapping=wave-per-row-tile")
+    before = ctx.kernel_launches
+    st = ctx._lib.swb_spmm(ctx._ctx, C.byref(o), 5, 4, 2 ** 31 - 100, 4, t[0].data_ptr(), t[1].data_ptr(),
+                           t[2].data_ptr(), B.data_ptr(), out.data_ptr(), None)
+    assert st == _lib.SWB_ERR_UNSUPPORTED and b"at most 2147483391 nonzeros" in ctx._lib.swb_last_error(ctx._ctx)
+    assert ctx.kernel_launches == before
 
 
 def test_accumulate_option(ctx):
