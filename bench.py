@@ -74,6 +74,8 @@ def parse_args():
                    "a CUDA graph of the steps")
     p.add_argument("--graph-steps", type=int, default=10, help="steps captured in one CUDA graph (inputs larger "
                    "than L2 only; the timed region stays exactly --steps steps)")
+    p.add_argument("--no-align", action="store_true", help="N > 1 with the L2 flush: do not line the ranks up "
+                   "(a 16-byte all-gather outside the event pairs) between a flush and the timed step")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu", action="store_true")
     p.add_argument("--no-parity", action="store_true", help="skip the comparison of the timed output with the oracle")
@@ -438,6 +440,15 @@ def measure_workload(args, env, name, *, headline, steps_arg, warmup, clocks=Non
     if local_input_bytes <= 2 * L2_BYTES:
         flush = env.setdefault("flush", torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device))
 
+    # The flush kernels of the ranks do not end at the same moment; a step's exchange would wait for the last of
+    # them inside its event pair.  A 16-byte all-gather between the flush and the first record lines the ranks
+    # up again, as consecutive steps of a real run do by themselves.
+    align = None
+    if flush is not None and world > 1 and getattr(ctx, "comm_world", 1) > 1 and not args.no_align:
+        tick = torch.zeros(4, dtype=torch.float32, device=device)
+        tock = torch.zeros(4 * world, dtype=torch.float32, device=device)
+        align = lambda: ctx.allgather(tick, tock)  # noqa: E731
+
     def timed(fn, calls):
         """Device time of `calls` calls in ms: one event pair around all of them, or one
         pair per call with an L2 flush outside the pairs."""
@@ -452,6 +463,8 @@ def measure_workload(args, env, name, *, headline, steps_arg, warmup, clocks=Non
         pairs = []
         for _ in range(calls):
             flush.zero_()
+            if align is not None:
+                align()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
@@ -527,6 +540,8 @@ def measure_workload(args, env, name, *, headline, steps_arg, warmup, clocks=Non
     for i in range(60):
         if flush is not None:
             flush.zero_()
+            if align is not None:
+                align()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         one_step()
@@ -615,7 +630,8 @@ def measure_workload(args, env, name, *, headline, steps_arg, warmup, clocks=Non
         "frac_of_hbm_peak": gbs / (peak * world), "bytes_algorithmic": wl["bytes"], "flops": wl["flops"],
         "gpu_launches": int(gpu_launches), "dispatch_stats": dispatch_stats, "device_status": device_status,
         "parity": parity,
-        "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps",
+        "l2": "inputs exceed L2" if flush is None else "256 MiB flush between timed steps" + (
+            "; ranks lined up by a 16-byte all-gather between the flush and the event pair" if align is not None else ""),
         "launch": (f"CUDA graph of {per_graph} step(s), replayed" if graph is not None else "host launch per step"),
     }
     if world > 1:
