@@ -180,8 +180,8 @@ SWB_API int swb_coo_spmv(swb_context *ctx, const swb_options *opts, int64_t rows
 
 /* sparsewave.spmm (SparseWaveOps.td:91-124): C[r, j] = sum_p val[p] *
  * B[col[p], j].  B is cols x n_rhs and C is rows x n_rhs, both row-major with
- * identity layout (SparseBenchmarkUtils.cpp:261-268).  The wave-per-row-tile
- * mapping takes at most 2^31 - 257 nonzeros (SWB_ERR_UNSUPPORTED beyond). */
+ * identity layout (SparseBenchmarkUtils.cpp:261-268).  At most 2^31 - 257
+ * nonzeros (SWB_ERR_UNSUPPORTED beyond). */
 SWB_API int swb_spmm(swb_context *ctx, const swb_options *opts, int64_t rows,
                      int64_t cols, int64_t nnz, int64_t n_rhs,
                      const int32_t *row_ptr, const int32_t *col_idx,

@@ -44,6 +44,43 @@ __global__ void spmm_thread_per_output_kernel(int64_t rows, int64_t N,
   C[e] = sum;
 }
 
+// The same mapping where N and the block size are multiples of 32: the 32 outputs of a warp lie in one
+// matrix row, so the warp reads 32 positions of col and val with one coalesced load each and passes them
+// around by shuffles instead of every lane loading every position (three L1 requests per position become
+// one).  Each thread still adds its products in position order: bit-identical to the kernel above.
+__global__ void spmm_thread_per_output_warp_row_kernel(int64_t rows, int64_t N,
+                                                       const int32_t *__restrict__ row_ptr,
+                                                       const int32_t *__restrict__ col,
+                                                       const float *__restrict__ val,
+                                                       const float *__restrict__ B, float *__restrict__ C) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= rows * N) return;  // rows * N is a multiple of 32: whole warps leave
+  const int lane = threadIdx.x & 31;
+  const int64_t row = e / N, j = e % N;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  const float *Bj = B + j;
+  float sum = 0.0f;
+  for (int base = start; base < end; base += 32) {
+    const int left = end - base < 32 ? end - base : 32;
+    const int cl = lane < left ? __ldg(col + base + lane) : 0;
+    const float vl = lane < left ? __ldg(val + base + lane) : 0.0f;
+    int k = 0;
+    for (; k + 4 <= left; k += 4) {
+      const int c0 = __shfl_sync(FULL, cl, k), c1 = __shfl_sync(FULL, cl, k + 1);
+      const int c2 = __shfl_sync(FULL, cl, k + 2), c3 = __shfl_sync(FULL, cl, k + 3);
+      const float b0 = __ldg(Bj + (int64_t)c0 * N), b1 = __ldg(Bj + (int64_t)c1 * N);
+      const float b2 = __ldg(Bj + (int64_t)c2 * N), b3 = __ldg(Bj + (int64_t)c3 * N);
+      sum = add(sum, mul(__shfl_sync(FULL, vl, k), b0));
+      sum = add(sum, mul(__shfl_sync(FULL, vl, k + 1), b1));
+      sum = add(sum, mul(__shfl_sync(FULL, vl, k + 2), b2));
+      sum = add(sum, mul(__shfl_sync(FULL, vl, k + 3), b3));
+    }
+    for (; k < left; ++k)
+      sum = add(sum, mul(__shfl_sync(FULL, vl, k), __ldg(Bj + (int64_t)__shfl_sync(FULL, cl, k) * N)));
+  }
+  C[e] = sum;
+}
+
 // ---------------------------------------------------------------------------
 // wave-per-row-tile (WavePerRowTileSpMMPattern, SparseWaveToGPU.cpp:1057-1256)
 // tiles = ceil(N / T); unit = blockIdx * (blockDim/32) + threadIdx/32;
@@ -577,8 +614,11 @@ cudaError_t launch_row_of_tiles(const CsrSpmmArgs &a, int block, cudaStream_t s)
 cudaError_t launch_spmm_thread_per_output(const CsrSpmmArgs &a, int block, cudaStream_t s,
                                           int64_t *launches) {
   SWB_GRID(grid, ceil_div(a.rows * a.n_rhs, block));
-  spmm_thread_per_output_kernel<<<grid, block, 0, s>>>(a.rows, a.n_rhs, a.row_ptr, a.col_idx,
-                                                       a.val, a.B, a.C);
+  if (a.n_rhs % 32 == 0 && block % 32 == 0)
+    spmm_thread_per_output_warp_row_kernel<<<grid, block, 0, s>>>(a.rows, a.n_rhs, a.row_ptr, a.col_idx, a.val, a.B,
+                                                                  a.C);
+  else
+    spmm_thread_per_output_kernel<<<grid, block, 0, s>>>(a.rows, a.n_rhs, a.row_ptr, a.col_idx, a.val, a.B, a.C);
   ++*launches;
   return cudaGetLastError();
 }

@@ -690,9 +690,9 @@ int swb_spmm(swb_context *ctx, const swb_options *o, int64_t rows, int64_t cols,
     return fail(ctx, SWB_ERR_INVALID_ARGUMENT, "spmm: NULL operand pointer");
   if (o->accumulate && o->spmm_mapping == SWB_THREAD_PER_OUTPUT)
     return fail(ctx, SWB_ERR_UNSUPPORTED, "accumulate is not available for the thread-per-output SpMM mapping");
-  // The wave kernels step through a row's positions in 32-bit strides of up to 128 past its end.
-  if (o->spmm_mapping == SWB_WAVE_PER_ROW_TILE && nnz > kI32Max - 256)
-    return fail(ctx, SWB_ERR_UNSUPPORTED, "spmm: the wave-per-row-tile mapping supports at most %lld nonzeros, but got %lld",
+  // The kernels step through a row's positions in 32-bit strides of up to 128 past its end.
+  if (nnz > kI32Max - 256)
+    return fail(ctx, SWB_ERR_UNSUPPORTED, "spmm: at most %lld nonzeros are supported, but got %lld",
                 (long long)(kI32Max - 256), (long long)nnz);
   swb_launch_shape shape;
   st = swb_launch_shape_query(ctx, o, rows, nnz, n_rhs, &shape);  // refuses grids beyond the CUDA limit

@@ -119,7 +119,7 @@ def test_argument_errors(ctx):
     before = ctx.kernel_launches
     st = ctx._lib.swb_spmm(ctx._ctx, C.byref(o), 5, 4, 2 ** 31 - 100, 4, t[0].data_ptr(), t[1].data_ptr(),
                            t[2].data_ptr(), B.data_ptr(), out.data_ptr(), None)
-    assert st == _lib.SWB_ERR_UNSUPPORTED and b"at most 2147483391 nonzeros" in ctx._lib.swb_last_error(ctx._ctx)
+    assert st == _lib.SWB_ERR_UNSUPPORTED and b"at most 2147483391 nonzeros are supported" in ctx._lib.swb_last_error(ctx._ctx)
     assert ctx.kernel_launches == before
 
 
