@@ -47,7 +47,7 @@ WORKLOADS = {
                name="c1: CSR SpMV 4096x4096, 16 nnz/row, f32/i32"),
     "c2": dict(kind="spmm", options="spmm-mapping=wave-per-row-tile spmm-tile-size=4 spmm-block-size=64",
                name="c2: CSR SpMM 65536x65536, 32 nnz/row, N=4, f32/i32"),
-    "c3": dict(kind="spmv", options="spmv-mapping=wave-per-position spmv-block-size=256",
+    "c3": dict(kind="spmv", options="spmv-mapping=wave-per-position spmv-block-size=128",
                name="c3: power-law CSR SpMV 4194304x4194304, Zipf(1.8) rows in [1,65536], f32/i32"),
     "c4": dict(kind="spmm", options="spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256",
                name="c4: CSR SpMM 2097152x2097152, 32 banded + 32 random nnz/row, N=64, f32/i32"),
