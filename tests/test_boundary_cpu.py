@@ -147,6 +147,17 @@ def test_launch_shapes_follow_reference_grid_arithmetic():
     assert s.logical_grid == 4096
     s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=64", 100, 1000, 70)
     assert s.work_units == 500 and s.physical_grid == s.logical_grid == 250  # ceil(70 / 16) = 5 tiles per row
+    # lanes per matrix row follow the mean row length: N = 64 with 5 per row takes half a warp per row (two rows
+    # per warp, 8 warps per block), with 13 per row the whole warp; N = 16 with 24 per row takes 8 lanes
+    s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", 1 << 20, 5 << 20, 64)
+    assert s.physical_grid == (1 << 20) // 2 // 8
+    s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", 1 << 20, 13 << 20, 64)
+    assert s.physical_grid == (1 << 20) // 8
+    s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=16 spmm-block-size=256", 1 << 20, 24 << 20, 16)
+    assert s.physical_grid == (1 << 20) // 4 // 8
+    # rows of B of 256, 384 and 512 floats: one warp per matrix row whatever the tile size says
+    s = swb.launch_shape("spmm-mapping=wave-per-row-tile spmm-tile-size=32 spmm-block-size=128", 1000, 64000, 512)
+    assert (s.work_units, s.physical_grid) == (16000, 250)
 
 
 def test_shard_rows_by_nnz():
