@@ -385,6 +385,73 @@ __global__ void spmm_wave_per_row_fused_kernel(int64_t rows, int64_t N, const in
   }
 }
 
+// Rows of B of 4 * G floats with G no power of two (N = 12, 20, 24, 28, 36 ... 124): the same fusion with
+// PG = 32 / G (rounded down) lane groups on PG * G of the warp's lanes; the other lanes only take part in the
+// shuffles.  The groups' partial sums are added into group 0 one after the other.
+__global__ void spmm_wave_per_row_any_kernel(int64_t rows, int64_t N, int G, const int32_t *__restrict__ row_ptr,
+                                             const int32_t *__restrict__ col, const float *__restrict__ val,
+                                             const float *__restrict__ B, float *__restrict__ C,
+                                             bool accumulate) {
+  const int PG = 32 / G;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bool active = lane < PG * G;
+  const int cq = lane % G, pg = active ? lane / G : 0;
+  const int start = row_ptr[row], end = row_ptr[row + 1];
+  const float *Bt = B + 4 * cq;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto fma4 = [&](float v, const float4 &b) {
+    acc.x = add(acc.x, mul(v, b.x)); acc.y = add(acc.y, mul(v, b.y));
+    acc.z = add(acc.z, mul(v, b.z)); acc.w = add(acc.w, mul(v, b.w));
+  };
+  int cn = start + lane < end ? __ldg(col + start + lane) : 0;
+  float vn = start + lane < end ? __ldg(val + start + lane) : 0.0f;
+  for (int base = start; base < end; base += 32) {
+    const int cl = cn;
+    const float vl = vn;
+    const int mine = base + 32 + lane;
+    cn = mine < end ? __ldg(col + mine) : 0;
+    vn = mine < end ? __ldg(val + mine) : 0.0f;
+    const int left = end - base < 32 ? end - base : 32;
+    int j = 0;  // warp-uniform
+    for (; j + 4 * PG <= left; j += 4 * PG) {
+      const int k = j + pg;
+      const int c0 = __shfl_sync(FULL, cl, k), c1 = __shfl_sync(FULL, cl, k + PG);
+      const int c2 = __shfl_sync(FULL, cl, k + 2 * PG), c3 = __shfl_sync(FULL, cl, k + 3 * PG);
+      const float v0 = __shfl_sync(FULL, vl, k), v1 = __shfl_sync(FULL, vl, k + PG);
+      const float v2 = __shfl_sync(FULL, vl, k + 2 * PG), v3 = __shfl_sync(FULL, vl, k + 3 * PG);
+      if (active) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N));
+        const float4 b1 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c1 * N));
+        const float4 b2 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c2 * N));
+        const float4 b3 = __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c3 * N));
+        fma4(v0, b0); fma4(v1, b1); fma4(v2, b2); fma4(v3, b3);
+      }
+    }
+    for (; j < left; j += PG) {
+      const int kk = j + pg;
+      const int c0 = __shfl_sync(FULL, cl, kk & 31);
+      const float v0 = __shfl_sync(FULL, vl, kk & 31);
+      if (active && kk < left) fma4(v0, __ldg(reinterpret_cast<const float4 *>(Bt + (int64_t)c0 * N)));
+    }
+  }
+  for (int g = 1; g < PG; ++g) {  // group g's sums into group 0, in group order
+    const int src = (lane + g * G) & 31;
+    const float tx = __shfl_sync(FULL, acc.x, src), ty = __shfl_sync(FULL, acc.y, src);
+    const float tz = __shfl_sync(FULL, acc.z, src), tw = __shfl_sync(FULL, acc.w, src);
+    if (lane < G) { acc.x = add(acc.x, tx); acc.y = add(acc.y, ty); acc.z = add(acc.z, tz); acc.w = add(acc.w, tw); }
+  }
+  if (lane < G) {
+    float4 *out = reinterpret_cast<float4 *>(C + row * N) + cq;
+    if (accumulate) {
+      const float4 old = *out;
+      acc.x = add(old.x, acc.x); acc.y = add(old.y, acc.y); acc.z = add(old.z, acc.z); acc.w = add(old.w, acc.w);
+    }
+    *out = acc;
+  }
+}
+
 // Rows of B of 128 * R floats (R = 2, 3, 4): the same fusion with the whole warp on one position; a lane
 // holds R float4 of the row of C (columns 4 * lane + 128 * r) and reads the position's row of B as R
 // coalesced 512-byte runs.  Two positions are in flight for R = 2, one for wider rows (as many bytes per
@@ -641,6 +708,15 @@ cudaError_t launch_spmm_wave_per_row_tile(const CsrSpmmArgs &a, int block, int t
       spmm_wave_per_row_wide_kernel<4><<<grid, block, 0, s>>>(a.rows, N, a.row_ptr, a.col_idx, a.val, a.B, a.C, a.accumulate);
     return cudaGetLastError();
   }
+  // other multiples of 4 up to 124 (rows of B of 12, 20, 24 ... floats) where a matrix row has enough positions
+  // for a warp: one warp per row as well
+  if (N >= 12 && N < 128 && N % 4 == 0 && !pow2_row && a.rows > 0 && a.nnz / a.rows >= 8 && aligned16(a.B) &&
+      aligned16(a.C)) {
+    SWB_GRID(grid, ceil_div(a.rows, block / 32));
+    spmm_wave_per_row_any_kernel<<<grid, block, 0, s>>>(a.rows, N, (int)(N / 4), a.row_ptr, a.col_idx, a.val, a.B,
+                                                       a.C, a.accumulate);
+    return cudaGetLastError();
+  }
   if (pow2_row && aligned16(a.B) && aligned16(a.C)) {
     if (N == 4) return launch_row_of_tiles<1>(a, block, s);
     if (N == 8) return launch_row_of_tiles<2>(a, block, s);
@@ -665,6 +741,8 @@ int64_t wave_per_row_tile_physical_grid(int64_t rows, int64_t nnz, int64_t n_rhs
   const int64_t wpb = block / 32;
   const bool pow2_row = n_rhs >= 4 && n_rhs <= 128 && (n_rhs & (n_rhs - 1)) == 0;
   if (n_rhs == 256 || n_rhs == 384 || n_rhs == 512) return max1(ceil_div(rows, wpb));
+  if (n_rhs >= 12 && n_rhs < 128 && n_rhs % 4 == 0 && !pow2_row && rows > 0 && nnz / rows >= 8)
+    return max1(ceil_div(rows, wpb));
   if (!pow2_row) return max1(ceil_div(rows * ceil_div(n_rhs, tile), wpb));
   if (n_rhs > 64) return max1(ceil_div(rows, wpb));
   const int64_t G = n_rhs / 4, mean = rows > 0 ? nnz / rows : 0;
