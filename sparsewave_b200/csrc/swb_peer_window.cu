@@ -29,6 +29,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -44,7 +45,8 @@ constexpr int64_t kHeaderBytes = 4096;
 // at 516, 1 + the buffer of the last finished step at 520 (0: none yet), finished steps per buffer at 524
 constexpr int kReadyOff = 0, kArrivalsOff = 256, kEpochOff = 512, kCountOff = 516, kLastBufferOff = 520, kFillsOff = 524;
 constexpr unsigned kPollLimit = 1u << 24;  // polls of a word in local memory, 100 ns apart (a few seconds), before giving up
-constexpr int kGridTarget = 256;           // CTAs of a step, split evenly over the destination ranks
+constexpr int kGridTarget = 128;           // CTAs of a step, split evenly over the destination ranks (four GPUs, 4 MB per rank:
+                                           // 28.8 us with 64 to 128 CTAs, 32.7 with 256 or more)
 
 struct PeerWindow {
   int ranks = 1, rank = 0, slices = 1;
@@ -208,7 +210,13 @@ int swb_comm_window_create(swb_context *ctx, int64_t bytes_per_rank, void **wind
   // rank is left waiting in a collective and no rank ends up with a window that a peer lacks.
   PeerWindow *w = new PeerWindow();
   w->ranks = ranks; w->rank = rank; w->bytes_per_rank = bytes_per_rank;
-  w->slices = kGridTarget / ranks > 0 ? kGridTarget / ranks : 1;
+  // SWB_WINDOW_CTAS (read at creation; the same on every rank, the arrival count relies on it): CTAs of a step
+  int grid_target = kGridTarget;
+  if (const char *env = getenv("SWB_WINDOW_CTAS")) {
+    const long v = strtol(env, nullptr, 10);
+    if (v >= ranks && v <= 1024) grid_target = (int)v;
+  }
+  w->slices = grid_target / ranks > 0 ? grid_target / ranks : 1;
   const size_t total = (size_t)kHeaderBytes + 2 * (size_t)ranks * (size_t)bytes_per_rank;  // header, two buffers
   struct Slot { cudaIpcMemHandle_t handle; int ok; int pad[3]; };  // one exchanged record, 80 bytes
   Slot *d_slots = nullptr;  // [0, ranks): gathered, [ranks]: this rank's
