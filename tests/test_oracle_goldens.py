@@ -132,3 +132,36 @@ def test_mismatch_counters():
     a = e + np.array([5e-5, 2e-4, 5e-3, 0], np.float32)
     assert oracle.count_mismatches_reference(a, e) == 1
     assert oracle.count_mismatches_bound(a, e, np.array([10.0, 10.0, 1000.0, 1.0]), rel=1e-5) == 1
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_against_scipy_in_float64(seed):
+    """An independent restatement: scipy.sparse in float64 on random ragged matrices.  The f32 loops of the
+    oracle (sequential, schedules of the position mappings, BSR) must lie within 1e-5 * sum|a b| of it."""
+    sp = pytest.importorskip("scipy.sparse")
+    rp, ci, v = random_csr(300, 257, 12, seed=seed, empty_fraction=0.2)
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1, 1, 257).astype(np.float32)
+    B = rng.uniform(-1, 1, (257, 9)).astype(np.float32)
+    A = sp.csr_matrix((v.astype(np.float64), ci, rp), shape=(300, 257))
+    absA = sp.csr_matrix((np.abs(v).astype(np.float64), ci, rp), shape=(300, 257))
+    want_y, bound_y = A @ x.astype(np.float64), absA @ np.abs(x).astype(np.float64)
+    for got in (oracle.csr_spmv(rp, ci, v, x), oracle.spmv_thread_position(rp, ci, v, x, chunk=8, segmented=True),
+                oracle.spmv_wave_position(rp, ci, v, x, block=64, batch=2)):
+        assert np.all(np.abs(got - want_y) <= 1e-5 * bound_y + 1e-30)
+    assert np.allclose(oracle.csr_abs_bound(rp, ci, v, x), bound_y, rtol=1e-5, atol=1e-30)
+    want_C, bound_C = A @ B.astype(np.float64), absA @ np.abs(B).astype(np.float64)
+    for got in (oracle.csr_spmm(rp, ci, v, B), oracle.spmm_thread_position(rp, ci, v, B, chunk=4)):
+        assert np.all(np.abs(got - want_C) <= 1e-5 * bound_C + 1e-30)
+    # BSR: 7 x 6 grid of 4 x 4 blocks, one block row empty
+    present = rng.random((7, 6)) < 0.4
+    present[3] = False
+    brp = np.zeros(8, np.int32)
+    brp[1:] = np.cumsum(present.sum(1))
+    bci = np.concatenate([np.nonzero(r)[0] for r in present]).astype(np.int32)
+    bv = rng.uniform(-1, 1, (len(bci), 4, 4)).astype(np.float32)
+    Bb = rng.uniform(-1, 1, (24, 5)).astype(np.float32)
+    M = sp.bsr_matrix((bv.astype(np.float64), bci, brp), shape=(28, 24))
+    absM = sp.bsr_matrix((np.abs(bv).astype(np.float64), bci, brp), shape=(28, 24))
+    got = oracle.bsr_spmm_f32(brp, bci, bv.reshape(-1), Bb, 4)
+    assert np.all(np.abs(got - M @ Bb.astype(np.float64)) <= 1e-5 * (absM @ np.abs(Bb).astype(np.float64)) + 1e-30)
